@@ -1,0 +1,278 @@
+"""The cache manager: pages of keys and values with a block table per request, groups of layers
+with pages of their own, and slots for per-request state of fixed size.
+
+Host-side bookkeeping is plain Python and runs without a GPU (device storage is only allocated
+when a device is given), so every decision here is tested on the CPU.
+
+Parity with InfiniLM: `python/infinilm/llm/cache_manager.py:71-364` (`BlockManager`: free list,
+pages handed out at allocation, given back when a request ends, `allocate_slots` / `append_slot`
+/ `free_blocks`), `:33-68` (`MambaCacheManager`: a pool of fixed-size state rows, row 0 kept as
+the zero state), `csrc/cache/kv_cache.cpp:113-148` (one tensor of pages per layer). Ours differs
+in that pages hold [K|V] of a page side by side, groups with a window give pages back as the
+window passes them, and no slot mapping is kept: a token's slot follows from block table and position.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence, Tuple
+
+from ..parts.spec import CacheNeed
+
+
+class OutOfPages(RuntimeError):
+    """A reservation needs more free pages (or state slots) than there are."""
+
+
+class CacheStateError(RuntimeError):
+    """A page or slot was freed twice, or a request was used after it was closed."""
+
+
+class PagePool:
+    """Page ids 0..n-1; first-in first-out reuse, so a page just freed is not the next one out."""
+
+    def __init__(self, n_pages: int):
+        self.n_pages = int(n_pages)
+        self._free: Deque[int] = deque(range(self.n_pages))
+        self._held = [False] * self.n_pages
+
+    @property
+    def n_free(self) -> int:
+        return len(self._free)
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise OutOfPages("no free page")
+        p = self._free.popleft()
+        self._held[p] = True
+        return p
+
+    def free(self, page: int) -> None:
+        if not (0 <= page < self.n_pages) or not self._held[page]:
+            raise CacheStateError(f"page {page} freed while not held")
+        self._held[page] = False
+        self._free.append(page)
+
+    def held(self) -> List[int]:
+        return [p for p, h in enumerate(self._held) if h]
+
+
+class StateSlots:
+    """Fixed-size per-request state: slot 0 is reserved as the zero state, 1..n-1 are handed out."""
+
+    def __init__(self, n_slots: int):
+        self.n_slots = int(n_slots)
+        self._free: Deque[int] = deque(range(1, self.n_slots))
+        self._held = [False] * self.n_slots
+
+    @property
+    def n_free(self) -> int:
+        return len(self._free)
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise OutOfPages("no free state slot")
+        s = self._free.popleft()
+        self._held[s] = True
+        return s
+
+    def free(self, slot: int) -> None:
+        if not (1 <= slot < self.n_slots) or not self._held[slot]:
+            raise CacheStateError(f"state slot {slot} freed while not held")
+        self._held[slot] = False
+        self._free.append(slot)
+
+
+@dataclass
+class CacheGroup:
+    """Run-order entries whose caches have the same geometry and policy share page ids:
+    one block table per (request, group), one storage tensor per entry."""
+    need: CacheNeed
+    entries: List[int]                            # run-order indices that own a cache in this group
+    pool: Optional[PagePool] = None               # paged_kv groups
+    storage: Dict[int, object] = field(default_factory=dict)   # run-order index -> device tensor
+
+
+@dataclass
+class SequenceCache:
+    """What the cache holds for one request."""
+    seq_id: object
+    length: int = 0                               # tokens whose keys/values (or state) are in the cache
+    tables: Dict[int, List[int]] = field(default_factory=dict)   # group -> page id per page index (-1: given back)
+    state_slot: int = 0
+    fresh_state: bool = True                      # no step has run yet: state groups start from the zero state
+    open: bool = True
+
+
+class CacheManager:
+    def __init__(self, needs: Sequence[Optional[CacheNeed]], page_size: int, num_pages: int, max_seqs: int,
+                 device=None, dtype=None, pages_per_group: Optional[Dict[int, int]] = None):
+        """`needs[i]` is what run-order entry i keeps (None: nothing). `num_pages` pages are made
+        for every paged group (or `pages_per_group[g]`); `max_seqs` bounds live requests."""
+        self.page_size, self.max_seqs = int(page_size), int(max_seqs)
+        if self.page_size <= 0 or (self.page_size & (self.page_size - 1)):
+            raise ValueError("page_size must be a power of two")
+        self.groups: List[CacheGroup] = []
+        self.group_of_entry: Dict[int, int] = {}
+        by_key: Dict[Tuple, int] = {}
+        for i, need in enumerate(needs):
+            if need is None:
+                continue
+            k = need.group_key()
+            if k not in by_key:
+                by_key[k] = len(self.groups)
+                self.groups.append(CacheGroup(need, []))
+            g = by_key[k]
+            self.groups[g].entries.append(i)
+            self.group_of_entry[i] = g
+        for g, grp in enumerate(self.groups):
+            if grp.need.kind == "paged_kv":
+                grp.pool = PagePool((pages_per_group or {}).get(g, num_pages))
+            elif grp.need.kind != "state":
+                raise ValueError(f"unknown cache kind {grp.need.kind!r}")
+        self.has_state = any(g.need.kind == "state" for g in self.groups)
+        self.slots = StateSlots(self.max_seqs + 1)
+        self.live: Dict[object, SequenceCache] = {}
+        self.device, self.dtype = device, dtype
+        if device is not None:
+            self._allocate_storage()
+
+    # -- device storage --------------------------------------------------------------------
+    def _allocate_storage(self) -> None:
+        import torch
+        for grp in self.groups:
+            n = grp.need
+            for i in grp.entries:
+                if n.kind == "paged_kv":
+                    shape = (grp.pool.n_pages, 2, n.n_kv_heads, self.page_size, n.head_dim)
+                    dt = self.dtype
+                else:
+                    shape = (self.slots.n_slots,) + tuple(n.shape)
+                    dt = torch.float32 if n.dtype == "float32" else self.dtype
+                grp.storage[i] = torch.zeros(shape, dtype=dt, device=self.device)
+
+    def bytes_per_token(self, elem_size: int) -> int:
+        b = 0
+        for grp in self.groups:
+            if grp.need.kind == "paged_kv":
+                b += len(grp.entries) * 2 * grp.need.n_kv_heads * grp.need.head_dim * elem_size
+        return b
+
+    # -- requests --------------------------------------------------------------------------
+    def open(self, seq_id) -> SequenceCache:
+        if seq_id in self.live:
+            raise CacheStateError(f"request {seq_id!r} is already open")
+        if len(self.live) >= self.max_seqs:
+            raise OutOfPages(f"{self.max_seqs} requests are live already")
+        seq = SequenceCache(seq_id, state_slot=self.slots.alloc())
+        for g, grp in enumerate(self.groups):
+            if grp.need.kind == "paged_kv":
+                seq.tables[g] = []
+        self.live[seq_id] = seq
+        return seq
+
+    def _first_needed_page(self, grp: CacheGroup, first_query_pos: int) -> int:
+        """Index of the first page a query at `first_query_pos` (or later) can still read."""
+        w = grp.need.window
+        if w is None:
+            return 0
+        return max(0, first_query_pos - w + 1) // self.page_size
+
+    def pages_needed(self, seq: SequenceCache, new_len: int) -> Dict[int, int]:
+        """How many new pages each paged group needs so that positions < new_len are covered."""
+        out = {}
+        n_idx = (new_len + self.page_size - 1) // self.page_size
+        for g, tbl in seq.tables.items():
+            out[g] = max(0, n_idx - len(tbl))
+        return out
+
+    def can_reserve(self, wants: Sequence[Tuple[SequenceCache, int]]) -> bool:
+        """Whether all of `wants` (request, new length) can be reserved together now."""
+        total: Dict[int, int] = {}
+        for seq, new_len in wants:
+            for g, n in self.pages_needed(seq, new_len).items():
+                total[g] = total.get(g, 0) + n
+        return all(self.groups[g].pool.n_free >= n for g, n in total.items())
+
+    def reserve(self, seq: SequenceCache, new_len: int) -> None:
+        """Grows the block tables so that positions < new_len have pages. All or nothing."""
+        self._check_open(seq)
+        if new_len < seq.length:
+            raise CacheStateError("a reservation cannot shrink a request")
+        need = self.pages_needed(seq, new_len)
+        for g, n in need.items():
+            if self.groups[g].pool.n_free < n:
+                raise OutOfPages(f"request {seq.seq_id!r} needs {n} more page(s) in cache group {g}, "
+                                 f"{self.groups[g].pool.n_free} are free")
+        for g, n in need.items():
+            for _ in range(n):
+                seq.tables[g].append(self.groups[g].pool.alloc())
+
+    def commit(self, seq: SequenceCache, new_len: int) -> None:
+        """The step that wrote positions < new_len has been issued: advance the length and give
+        back pages that a window has passed (no later query can read them)."""
+        self._check_open(seq)
+        seq.length = new_len
+        seq.fresh_state = False
+        for g, tbl in seq.tables.items():
+            grp = self.groups[g]
+            first = self._first_needed_page(grp, new_len)
+            for idx in range(min(first, len(tbl))):
+                if tbl[idx] >= 0:
+                    grp.pool.free(tbl[idx])
+                    tbl[idx] = -1
+
+    def close(self, seq: SequenceCache) -> None:
+        """The request is finished: all it holds is given back."""
+        self._check_open(seq)
+        for g, tbl in seq.tables.items():
+            for p in tbl:
+                if p >= 0:
+                    self.groups[g].pool.free(p)
+            tbl.clear()
+        self.slots.free(seq.state_slot)
+        seq.open = False
+        del self.live[seq.seq_id]
+
+    def _check_open(self, seq: SequenceCache) -> None:
+        if not seq.open or self.live.get(seq.seq_id) is not seq:
+            raise CacheStateError(f"request {seq.seq_id!r} is not open")
+
+    # -- views -----------------------------------------------------------------------------
+    def free_pages(self) -> Dict[int, int]:
+        return {g: grp.pool.n_free for g, grp in enumerate(self.groups) if grp.pool is not None}
+
+    def check_invariants(self) -> None:
+        """No page lost, none held twice: used by tests and debug runs."""
+        for g, grp in enumerate(self.groups):
+            if grp.pool is None:
+                continue
+            held = []
+            for seq in self.live.values():
+                held += [p for p in seq.tables[g] if p >= 0]
+            if len(held) != len(set(held)):
+                raise CacheStateError(f"group {g}: a page is held twice")
+            if sorted(held) != grp.pool.held():
+                raise CacheStateError(f"group {g}: pages held by requests differ from the pool's record")
+            if len(held) + grp.pool.n_free != grp.pool.n_pages:
+                raise CacheStateError(f"group {g}: a page is lost")
+
+
+@dataclass
+class PagedKVView:
+    """What a mixer sees of a paged cache in one step."""
+    storage: object                               # [pages, 2, kv_heads, page_size, head_dim]
+    block_table: object                           # int32 [entries, width] on the device
+    page_size: int
+    writable: bool = True
+    max_pages: int = 0                            # width in use this step
+
+
+@dataclass
+class StateView:
+    """What a mixer sees of a state group in one step: read from `read_slots` (slot 0, the zero
+    state, for a request's first step), write to `write_slots`."""
+    storage: object                               # [slots, *shape]
+    read_slots: object                            # int32 [entries]
+    write_slots: object                           # int32 [entries]
+    writable: bool = True

@@ -1,0 +1,68 @@
+// Shared helpers of the sm_100a kernels: element conversion, reductions, launch checks.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define IL_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Element kinds passed from the host as integers.
+enum { IL_F32 = 0, IL_BF16 = 1 };
+
+// Error codes returned by the entry points (0 = launched).
+enum { IL_OK = 0, IL_BAD_ARG = -1, IL_UNSUPPORTED = -2 };
+
+#define IL_LAUNCH_CHECK()                                         \
+    do {                                                          \
+        cudaError_t e__ = cudaGetLastError();                     \
+        if (e__ != cudaSuccess) return 1000 + (int)e__;           \
+    } while (0)
+
+__device__ __forceinline__ float il_to_f(float x) { return x; }
+__device__ __forceinline__ float il_to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T il_from_f(float x);
+template <> __device__ __forceinline__ float il_from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 il_from_f<__nv_bfloat16>(float x) {
+    return __float2bfloat16_rn(x);
+}
+
+// Reads element i of a vector stored as f32 or bf16.
+__device__ __forceinline__ float il_load_any(const void* p, int kind, size_t i) {
+    return kind == IL_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+
+__device__ __forceinline__ float il_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float il_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `sh` holds 32 floats.
+__device__ __forceinline__ float il_block_sum(float v, float* sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nw = (blockDim.x + 31) >> 5;
+    v = il_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? sh[lane] : 0.f;
+    t = il_warp_sum(t);
+    return t;
+}
+__device__ __forceinline__ float il_block_max(float v, float* sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nw = (blockDim.x + 31) >> 5;
+    v = il_warp_max(v);
+    __syncthreads();
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? sh[lane] : -INFINITY;
+    t = il_warp_max(t);
+    return t;
+}

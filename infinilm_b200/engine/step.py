@@ -1,0 +1,239 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A step takes any mix of prompt portions and single decoded tokens, cut anywhere. It runs only
+the tokens it is given, as one batch, reading earlier tokens from the cache, and returns the
+float32 logits at the places asked for. The logits at a position do not depend on how the
+tokens were cut into steps or on what else is in the batch, beyond rounding.
+
+Parity with InfiniLM: `csrc/engine/infer_engine.hpp:53` / `csrc/models/infinilm_model.hpp:20-67`
+(`forward(Input) -> Output`; Input carries input_ids, position_ids, past/total lengths,
+input_offsets, block_tables, slot_mapping), `python/infinilm/processors/basic_llm_processor.py:161-263`
+(how a batch is flattened). Here positions, lengths and slots are derived from three small
+arrays per step (token ids, per-token position and entry, per-entry block-table rows) that go to
+the device in one copy, and the head runs only on the wanted rows.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages, PagedKVView, SequenceCache, StateView
+from ..models.causal_lm import CausalLM
+
+
+class StepError(ValueError):
+    """A batch that cannot be run: says which entry and why."""
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens, and the places among them (indices into
+    `tokens`) whose logits are wanted."""
+    seq: SequenceCache
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class Workspace:
+    """Device buffers that live as long as the engine; a buffer is named by its use and sized
+    for the largest step, so no step allocates."""
+
+    def __init__(self, device, max_tokens: int):
+        self.device, self.max_tokens = device, int(max_tokens)
+        self._bufs: Dict[tuple, torch.Tensor] = {}
+
+    def rows(self, tag: str, n: int, width: int, dtype: torch.dtype) -> torch.Tensor:
+        key = (tag, width, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.shape[0] < n:
+            cap = max(n, self.max_tokens if buf is None else buf.shape[0] * 2)
+            buf = torch.empty((cap, width), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n]
+
+    def flat(self, tag: str, n: int, dtype: torch.dtype) -> torch.Tensor:
+        key = (tag, "flat", dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1024), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n]
+
+
+@dataclass
+class StepContext:
+    """What the parts see of a step. Device arrays are int32."""
+    dtype: torch.dtype
+    T: int
+    n_entries: int
+    n_decode: int                                 # the first n_decode entries bring one token each
+    token_ids: torch.Tensor                       # [T]
+    tok_pos: torch.Tensor                         # [T] absolute position of each token in its request
+    tok_entry: torch.Tensor                       # [T] entry index of each token
+    entry_qstart: torch.Tensor                    # [E+1] first token row of each entry
+    entry_kvlen: torch.Tensor                     # [E] tokens in cache after this step (start + q_len)
+    want_rows: torch.Tensor                       # [n_want] token rows whose logits are wanted
+    n_want: int
+    ws: Workspace
+    h_qlen: List[int] = field(default_factory=list)     # host copies for launch planning
+    h_kvlen: List[int] = field(default_factory=list)
+    max_qlen: int = 0
+    max_kvlen: int = 0
+    tap: Optional[Callable] = None                # debug hook: tap(name, resid, pending)
+
+
+class StepRunner:
+    """Owns the model, the cache manager and the device buffers, and runs steps."""
+
+    def __init__(self, model: CausalLM, cache: CacheManager, device, max_batch_tokens: int):
+        self.model, self.cache, self.device = model, cache, torch.device(device)
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.ws = Workspace(self.device, self.max_batch_tokens)
+        self.dtype = model.dtype
+        self._desc_dev: Optional[torch.Tensor] = None
+        self.tap: Optional[Callable] = None
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # -- descriptor buffers ----------------------------------------------------------------
+    def _desc(self, n_ints: int):
+        """A pinned host buffer (one of a small ring, so the copy of an earlier step is never
+        overwritten while in flight) and the device buffer the kernels read."""
+        if self._desc_dev is None or self._desc_dev.numel() < n_ints:
+            cap = max(n_ints, 1 << 16)
+            if self._desc_dev is not None:
+                torch.cuda.current_stream(self.device).synchronize()
+            self._desc_ring = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+            self._desc_events = [None] * 4
+            self._desc_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self._desc_i = (getattr(self, "_desc_i", -1) + 1) % 4
+        ev = self._desc_events[self._desc_i]
+        if ev is not None:
+            ev.synchronize()
+        return self._desc_ring[self._desc_i], self._desc_dev
+
+    # -- the step ----------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the order of
+        `entries` and of each entry's `want`."""
+        if not entries:
+            return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.device)
+        vocab = self.model.vocab
+        seen = set()
+        T = 0
+        max_pos = getattr(self, "max_positions", None)
+        for i, e in enumerate(entries):
+            n = len(e.tokens)
+            if n < 1:
+                raise StepError(f"entry {i} ({e.seq.seq_id!r}) brings no token")
+            if id(e.seq) in seen:
+                raise StepError(f"request {e.seq.seq_id!r} appears twice in one step")
+            seen.add(id(e.seq))
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise StepError(f"entry {i} ({e.seq.seq_id!r}): wanted place {w} is outside its {n} tokens")
+            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                raise StepError(f"request {e.seq.seq_id!r}: token id outside [0, {vocab})")
+            if max_pos is not None and e.seq.length + n > max_pos:
+                raise StepError(f"request {e.seq.seq_id!r} would pass max_position_embeddings {max_pos}")
+            T += n
+        if T > self.max_batch_tokens:
+            raise StepError(f"step of {T} tokens exceeds max_batch_tokens {self.max_batch_tokens}")
+        # Reserve pages for all entries, or for none.
+        if not self.cache.can_reserve([(e.seq, e.seq.length + len(e.tokens)) for e in entries]):
+            raise OutOfPages("the step needs more pages than are free: "
+                             + ", ".join(f"{e.seq.seq_id!r}+{len(e.tokens)}" for e in entries))
+        for e in entries:
+            self.cache.reserve(e.seq, e.seq.length + len(e.tokens))
+
+        # Single decoded tokens first, prompt portions after; the wanted rows keep the caller's order.
+        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
+        n_decode = sum(1 for e in entries if len(e.tokens) == 1)
+        E = len(entries)
+        qstart = [0] * (E + 1)
+        row_of_entry = {}
+        for k, i in enumerate(order):
+            row_of_entry[i] = k
+            qstart[k + 1] = qstart[k] + len(entries[i].tokens)
+        want_rows: List[int] = []
+        for i, e in enumerate(entries):
+            base = qstart[row_of_entry[i]]
+            want_rows.extend(base + w for w in e.want)
+        n_want = len(want_rows)
+
+        groups = self.cache.groups
+        paged = [g for g, grp in enumerate(groups) if grp.need.kind == "paged_kv"]
+        widths = {}
+        for g in paged:
+            widths[g] = max(1, max(len(e.seq.tables[g]) for e in entries))
+        n_ints = 3 * T + (E + 1) + E + max(n_want, 1) + 2 * E + sum(E * w for w in widths.values())
+        host, dev = self._desc(n_ints)
+        h = host.numpy()
+        off = 0
+
+        def take(n):
+            nonlocal off
+            v = (off, off + n)
+            off += n
+            return v
+        s_tok, s_pos, s_ent = take(T), take(T), take(T)
+        s_qs, s_kv, s_want, s_rs, s_wsl = take(E + 1), take(E), take(max(n_want, 1)), take(E), take(E)
+        s_bt = {g: take(E * widths[g]) for g in paged}
+        h_qlen, h_kvlen = [], []
+        for k, i in enumerate(order):
+            e = entries[i]
+            n, start = len(e.tokens), e.seq.length
+            a, b = qstart[k], qstart[k + 1]
+            h[s_tok[0] + a: s_tok[0] + b] = np.asarray(e.tokens, dtype=np.int64)
+            h[s_pos[0] + a: s_pos[0] + b] = np.arange(start, start + n, dtype=np.int32)
+            h[s_ent[0] + a: s_ent[0] + b] = k
+            h[s_kv[0] + k] = start + n
+            h[s_rs[0] + k] = 0 if e.seq.fresh_state else e.seq.state_slot
+            h[s_wsl[0] + k] = e.seq.state_slot
+            h_qlen.append(n)
+            h_kvlen.append(start + n)
+            for g in paged:
+                w = widths[g]
+                tbl = e.seq.tables[g]
+                row = h[s_bt[g][0] + k * w: s_bt[g][0] + (k + 1) * w]
+                row[:len(tbl)] = tbl
+                row[len(tbl):] = -1
+        h[s_qs[0]: s_qs[1]] = qstart
+        if n_want:
+            h[s_want[0]: s_want[0] + n_want] = want_rows
+        dev[:off].copy_(host[:off], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._desc_events[self._desc_i] = ev
+
+        def view(s):
+            return dev[s[0]: s[1]]
+        ctx = StepContext(
+            dtype=self.dtype, T=T, n_entries=E, n_decode=n_decode, token_ids=view(s_tok), tok_pos=view(s_pos),
+            tok_entry=view(s_ent), entry_qstart=view(s_qs), entry_kvlen=view(s_kv),
+            want_rows=dev[s_want[0]: s_want[0] + n_want], n_want=n_want, ws=self.ws,
+            h_qlen=h_qlen, h_kvlen=h_kvlen, max_qlen=max(h_qlen), max_kvlen=max(h_kvlen), tap=self.tap)
+
+        caches = []
+        for i, st in enumerate(self.model.order):
+            owner = i if st.cache_from is None else st.cache_from
+            g = self.cache.group_of_entry.get(owner)
+            if g is None:
+                caches.append(None)
+                continue
+            grp = groups[g]
+            if grp.need.kind == "paged_kv":
+                caches.append(PagedKVView(grp.storage[owner], view(s_bt[g]).view(E, widths[g]), self.cache.page_size,
+                                          writable=(owner == i), max_pages=widths[g]))
+            else:
+                caches.append(StateView(grp.storage[owner], view(s_rs), view(s_wsl), writable=(owner == i)))
+
+        logits = self.model.forward(ctx, caches)
+        for e in entries:
+            self.cache.commit(e.seq, e.seq.length + len(e.tokens))
+        self.steps_run += 1
+        self.tokens_run += T
+        return logits

@@ -1,0 +1,199 @@
+"""Python face of the hand-written sm_100a kernels.
+
+Each function checks its arguments on the host (shapes, dtypes, contiguity, device), then calls
+the `extern "C"` entry point of the kernel's shared object with raw device pointers and the
+current CUDA stream. There is no CPU implementation and no library stand-in here: a tensor that
+is not on a CUDA device, or a kernel library that cannot be built, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def kind_of(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
+    if t is None:
+        return _c_void_p(0)
+    return _c_void_p(t.data_ptr())
+
+
+def _stream() -> _c_void_p:
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("infinilm_b200 kernels run on a CUDA device only; got a tensor on "
+                              f"{t.device} (there is no CPU path)")
+
+
+def _contig(name: str, t: torch.Tensor) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: bad argument")
+    if code == -2:
+        raise KernelError(f"{what}: size not supported by this kernel")
+    if code >= 1000:
+        raise KernelError(f"{what}: CUDA launch failed (cudaError {code - 1000})")
+    raise KernelError(f"{what}: error {code}")
+
+
+_sigs_done = set()
+
+
+def _fn(lib_name: str, fn_name: str, argtypes, defines=None):
+    lib = build.load(lib_name, defines)
+    f = getattr(lib, fn_name)
+    key = (id(lib), fn_name)
+    if key not in _sigs_done:
+        f.argtypes = argtypes
+        f.restype = _c_int
+        _sigs_done.add(key)
+    return f
+
+
+# ----------------------------------------------------------------------------------------------
+def embed(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor, round_bf16: bool) -> None:
+    """out[t,:] (f32) = table[ids[t],:] * scale; rounded through bfloat16 when `round_bf16`."""
+    _need_cuda(ids, table, out)
+    T, (V, H) = ids.numel(), table.shape
+    if ids.dtype != torch.int32 or out.dtype != torch.float32 or out.shape != (T, H):
+        raise KernelError("embed: ids int32 [T], out float32 [T,H]")
+    _contig("table", table), _contig("out", out)
+    f = _fn("embedding", "il_embed", [_c_void_p, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int,
+                                      _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(ids), _ptr(table), kind_of(table.dtype), scale, _ptr(out), T, H, V, int(round_bf16),
+             _stream()), "embed")
+
+
+def add_rmsnorm(resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scale: float, weight: torch.Tensor,
+                eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """resid += branch_scale * branch (f32, in place); out = RMSNorm(resid) * weight.
+
+    With `rows` (int32 indices) only those rows are normalised, into out[0..len(rows)), and
+    `resid` is left as it was."""
+    _need_cuda(resid, branch, weight, out, rows)
+    T, H = resid.shape
+    n = T if rows is None else rows.numel()
+    if resid.dtype != torch.float32 or weight.numel() != H or out.shape[-1] != H or out.shape[0] < n:
+        raise KernelError("add_rmsnorm: resid float32 [T,H], weight [H], out [n,H]")
+    if branch is not None and (branch.shape != resid.shape or branch.dtype != out.dtype):
+        raise KernelError("add_rmsnorm: branch must match resid's shape and out's dtype")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("add_rmsnorm: rows must be int32")
+    _contig("resid", resid), _contig("out", out)
+    if branch is not None:
+        _contig("branch", branch)
+    f = _fn("rmsnorm", "il_add_rmsnorm", [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_float, _c_void_p,
+                                          _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(resid), _ptr(branch), branch_scale, _ptr(weight), kind_of(weight.dtype), eps, _ptr(out),
+             kind_of(out.dtype), _ptr(rows), n, H, _stream()), "add_rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t,i] = silu(gate_up[t,i]) * gate_up[t,I+i]."""
+    _need_cuda(gate_up, out)
+    T, I2 = gate_up.shape
+    if I2 % 2 or out.shape != (T, I2 // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("swiglu: gate_up [T,2I], out [T,I] of the same dtype")
+    _contig("gate_up", gate_up), _contig("out", out)
+    f = _fn("swiglu", "il_swiglu", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), kind_of(out.dtype), T, I2 // 2, _stream()), "swiglu")
+
+
+def add_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
+    _need_cuda(y, bias)
+    T, N = y.shape
+    if bias.numel() != N:
+        raise KernelError("add_bias: bias [N]")
+    _contig("y", y)
+    f = _fn("swiglu", "il_add_bias", [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(y), kind_of(y.dtype), _ptr(bias), kind_of(bias.dtype), T, N, _stream()), "add_bias")
+
+
+def rope_store(qkv: torch.Tensor, tok_pos: torch.Tensor, tok_entry: torch.Tensor, block_table: torch.Tensor,
+               cache: Optional[torch.Tensor], page_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
+               rot_dim: int, inv_freq: Optional[torch.Tensor], mscale: float) -> None:
+    """Rotates q and k of `qkv` in place and writes k and v to their cache slots (if `cache`)."""
+    _need_cuda(qkv, tok_pos, tok_entry, block_table, cache, inv_freq)
+    T = qkv.shape[0]
+    _contig("qkv", qkv), _contig("block_table", block_table)
+    if tok_pos.dtype != torch.int32 or tok_entry.dtype != torch.int32 or block_table.dtype != torch.int32:
+        raise KernelError("rope_store: descriptors must be int32")
+    if rot_dim > 0 and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2):
+        raise KernelError("rope_store: inv_freq float32 [rot_dim/2]")
+    if cache is not None:
+        _contig("cache", cache)
+        if cache.dtype != qkv.dtype or tuple(cache.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+            raise KernelError("rope_store: cache [pages,2,kv_heads,page,head_dim] of qkv's dtype")
+    f = _fn("rope_cache", "il_rope_store", [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                            _c_float, _c_void_p])
+    _check(f(_ptr(qkv), kind_of(qkv.dtype), qkv.shape[1], _ptr(tok_pos), _ptr(tok_entry), _ptr(block_table),
+             block_table.shape[1], _ptr(cache), page_size, T, n_heads, n_kv_heads, head_dim, rot_dim,
+             _ptr(inv_freq), mscale, _stream()), "rope_store")
+
+
+def attention_plain(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                    tok_pos: torch.Tensor, tok_entry: torch.Tensor, page_size: int, n_heads: int,
+                    n_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None) -> None:
+    """Causal attention of every token of `qkv` over its request's cache pages (plain kernel)."""
+    _need_cuda(qkv, out, cache, block_table, tok_pos, tok_entry)
+    T = qkv.shape[0]
+    if out.shape != (T, n_heads * head_dim) or out.dtype != qkv.dtype or cache.dtype != qkv.dtype:
+        raise KernelError("attention_plain: out [T, heads*head_dim], same dtype as qkv and cache")
+    if head_dim > 256:
+        raise KernelError(f"attention_plain: head_dim {head_dim} > 256 is not supported")
+    _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
+    f = _fn("attn_plain", "il_attn_plain", [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                            _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                            _c_int, _c_void_p])
+    _check(f(_ptr(qkv), kind_of(qkv.dtype), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table),
+             block_table.shape[1], _ptr(tok_pos), _ptr(tok_entry), page_size, T, n_heads, n_kv_heads, head_dim,
+             scale, int(window or 0), _stream()), "attention_plain")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
+             bias: Optional[torch.Tensor] = None) -> None:
+    """out[M,N] = alpha * a[M,K] @ w[N,K]^T (+ bias), all float32, FP32 pipes only."""
+    _need_cuda(a, w, out, bias)
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.float32 or w.dtype != torch.float32 or out.dtype != torch.float32:
+        raise KernelError("gemm_f32: float32 tensors")
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_f32: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_f32: innermost dimension must be contiguous")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_f32: bias float32 [N]")
+    f = _fn("gemm_f32", "il_gemm_f32", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_float,
+                                        _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _ptr(bias), alpha, M, N, K,
+             _stream()), "gemm_f32")

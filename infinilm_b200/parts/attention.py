@@ -1,0 +1,84 @@
+"""Grouped-query attention over the paged cache.
+
+Parity with InfiniLM: `csrc/layers/attention/attention.cpp:7-46` (fused QKV projection, o_proj,
+scale 1/sqrt(head_dim)), `:96-137` (project, view as heads, rotate q and k in place, attend,
+project out), `csrc/layers/attention/backends/paged_attn.cpp:20-84` (write k/v to their slots,
+then attend over the pages), `csrc/layers/linear/fused_linear.cpp:57-71,102-110` (q, k, v are row
+ranges of one weight).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from .base import Mixer, build_part, register_part
+from .linear import Linear
+from .spec import CacheNeed, PartSpec, WeightSpec
+
+
+class Attention(Mixer):
+    """params: hidden, n_heads, n_kv_heads, head_dim, qkv_bias, out_bias, out_scale,
+    window (None = all keys), position (PartSpec of a position encoding)."""
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        p = params
+        self.hidden, self.nh, self.nkv, self.hd = int(p["hidden"]), int(p["n_heads"]), int(p["n_kv_heads"]), int(p["head_dim"])
+        if self.nh % self.nkv:
+            raise ValueError(f"attention: {self.nh} heads are not a multiple of {self.nkv} kv heads")
+        if self.hd % 16 or not 16 <= self.hd <= 256:
+            raise ValueError(f"attention: head_dim {self.hd} is not supported (multiples of 16 from 16 to 256)")
+        self.qkv_bias, self.out_bias = bool(p.get("qkv_bias", False)), bool(p.get("out_bias", False))
+        self.window: Optional[int] = p.get("window")
+        self.scale = 1.0 / math.sqrt(self.hd)
+        self.n_qkv = (self.nh + 2 * self.nkv) * self.hd
+        self.qkv = Linear(self.hidden, self.n_qkv, dtype)
+        self.o_proj = Linear(self.nh * self.hd, self.hidden, dtype, alpha=float(p.get("out_scale", 1.0)))
+        pos: PartSpec = p.get("position") or PartSpec("none")
+        self.position = build_part("position", pos, dtype)
+        if self.position.rot_dim > self.hd:
+            raise ValueError("attention: rotary dim exceeds head_dim")
+
+    def weight_specs(self) -> List[WeightSpec]:
+        hd, H = self.hd, self.hidden
+        specs = [WeightSpec("q_proj.weight", (self.nh * hd, H)), WeightSpec("k_proj.weight", (self.nkv * hd, H)),
+                 WeightSpec("v_proj.weight", (self.nkv * hd, H)), WeightSpec("o_proj.weight", (H, self.nh * hd))]
+        if self.qkv_bias:
+            specs += [WeightSpec("q_proj.bias", (self.nh * hd,), "vector"), WeightSpec("k_proj.bias", (self.nkv * hd,), "vector"),
+                      WeightSpec("v_proj.bias", (self.nkv * hd,), "vector")]
+        if self.out_bias:
+            specs.append(WeightSpec("o_proj.bias", (H,), "vector"))
+        return specs
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        w = torch.cat([t["q_proj.weight"], t["k_proj.weight"], t["v_proj.weight"]], dim=0)
+        b = None
+        if self.qkv_bias:
+            b = torch.cat([t["q_proj.bias"].float(), t["k_proj.bias"].float(), t["v_proj.bias"].float()])
+        self.qkv.set(w, b)
+        self.o_proj.set(t["o_proj.weight"], t.get("o_proj.bias"))
+        self.position.to_device(w.device)
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed("paged_kv", n_kv_heads=self.nkv, head_dim=self.hd, window=self.window)
+
+    def forward(self, x, ctx, cache):
+        T = x.shape[0]
+        qkv = self.qkv(x, ctx.ws.rows("qkv", T, self.n_qkv, self.dtype))
+        pos = self.position
+        ops.rope_store(qkv, ctx.tok_pos, ctx.tok_entry, cache.block_table,
+                       cache.storage if cache.writable else None, cache.page_size,
+                       self.nh, self.nkv, self.hd, pos.rot_dim, pos.inv_freq, pos.mscale)
+        out = ctx.ws.rows("attn_out", T, self.nh * self.hd, self.dtype)
+        self.attend(qkv, out, ctx, cache)
+        return self.o_proj(out, ctx.ws.rows("branch", T, self.hidden, self.dtype))
+
+    def attend(self, qkv, out, ctx, cache) -> None:
+        ops.attention_plain(qkv, out, cache.storage, cache.block_table, ctx.tok_pos, ctx.tok_entry,
+                            cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window)
+
+
+register_part("mixer", "attention", Attention)

@@ -1,0 +1,128 @@
+"""Interfaces of the parts a layer is put together from, and the registries that name them.
+
+A part is built from its parameters alone (`PartSpec.params`); it never learns which model it is
+in. Five kinds of part exist, each with its own registry:
+
+  norm              `add_norm(resid, branch, branch_scale, out, rows=None)`
+  position          rotation tables for a mixer (`inv_freq`, `mscale`, `rot_dim`)
+  mixer             `forward(x, ctx, cache) -> y`, `cache_need()`
+  feed_forward      `forward(x, ctx) -> y`
+  arrangement       a block of two norms, a mixer and a feed-forward: `run(resid, pending, ctx, cache)`
+
+Every part lists the checkpoint tensors it wants (`weight_specs`) and receives them, already on
+the device, through `set_weights`.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, List, Optional
+
+import torch
+
+from .spec import CacheNeed, PartSpec, WeightSpec
+
+
+class Part:
+    """Common base: parameters in, list of wanted tensors out, tensors in."""
+
+    def __init__(self, params: Dict[str, Any], prefix: str, dtype: torch.dtype):
+        self.params = dict(params)
+        self.prefix = prefix
+        self.dtype = dtype                       # compute dtype: torch.float32 or torch.bfloat16
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def set_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """`tensors` maps local names to device tensors (matrices already in the compute dtype)."""
+
+    def full_name(self, local: str) -> str:
+        return f"{self.prefix}.{local}" if self.prefix else local
+
+
+class Norm(Part):
+    def add_norm(self, resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scale: float,
+                 out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """resid (f32 [T,H]) += branch_scale * branch; out = norm(resid). With `rows`, only those
+        rows are normalised into out[0:len(rows)] and resid is left alone."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """A position encoding that a mixer applies to its queries and keys."""
+    rot_dim: int = 0
+    mscale: float = 1.0
+    inv_freq: Optional[torch.Tensor] = None     # float32 [rot_dim/2] on the device
+
+    def to_device(self, device: torch.device) -> None:
+        pass
+
+
+class Mixer(Part):
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        """x [T,H] in the compute dtype -> y [T,H]. `cache` is this run entry's view of the cache
+        (`PagedKVView`, `StateView` or None); `cache.writable` is False when the entry reads
+        another entry's cache."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Arrangement:
+    """How the parts of one layer are wired around the residual stream."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward, params: Dict[str, Any]):
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+        self.params = dict(params)
+
+    def parts(self) -> List[Part]:
+        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def run(self, resid: torch.Tensor, pending, ctx, cache):
+        """`pending` is (branch, scale) not yet added to `resid`, or None. Returns the new pending."""
+        raise NotImplementedError
+
+
+_REGISTRIES: Dict[str, Dict[str, Callable]] = {
+    "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {}, "embedding": {}, "head": {},
+}
+
+
+def register_part(family: str, kind: str, cls: Callable) -> None:
+    """Register `cls` under `kind` in one of the families above. A test or a new architecture
+    calls this for its own parts; nothing else in the framework has to change."""
+    if family not in _REGISTRIES:
+        raise KeyError(f"unknown part family {family!r} ({', '.join(_REGISTRIES)})")
+    _REGISTRIES[family][kind] = cls
+
+
+def unregister_part(family: str, kind: str) -> None:
+    _REGISTRIES[family].pop(kind, None)
+
+
+def part_class(family: str, kind: str) -> Callable:
+    _ensure_builtin()
+    try:
+        return _REGISTRIES[family][kind]
+    except KeyError:
+        raise KeyError(f"no {family} part of kind {kind!r} is registered "
+                       f"(known: {', '.join(sorted(_REGISTRIES[family]))})") from None
+
+
+def build_part(family: str, spec: PartSpec, dtype: torch.dtype):
+    return part_class(family, spec.kind)(spec.params, spec.prefix, dtype)
+
+
+_builtin_done = False
+
+
+def _ensure_builtin() -> None:
+    global _builtin_done
+    if not _builtin_done:
+        _builtin_done = True
+        from . import attention, blocks, embedding, feed_forward, norms, position  # noqa: F401

@@ -1,0 +1,50 @@
+"""Dense SwiGLU feed-forward: down(silu(gate(x)) * up(x)).
+
+Parity with InfiniLM: `csrc/layers/mlp/mlp.cpp:7-38` (gate and up as one product, `swiglu(up, gate)`,
+then down), `csrc/layers/linear/fused_linear.cpp:152-158,177-185` (gate rows first, up rows second).
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import ops
+from .base import FeedForward, register_part
+from .linear import Linear
+from .spec import WeightSpec
+
+
+class SwiGLU(FeedForward):
+    """params: hidden, intermediate, bias, out_scale."""
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        self.hidden, self.inter = int(params["hidden"]), int(params["intermediate"])
+        self.bias = bool(params.get("bias", False))
+        self.gate_up = Linear(self.hidden, 2 * self.inter, dtype)
+        self.down = Linear(self.inter, self.hidden, dtype, alpha=float(params.get("out_scale", 1.0)))
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [WeightSpec("gate_proj.weight", (self.inter, self.hidden)), WeightSpec("up_proj.weight", (self.inter, self.hidden)),
+                 WeightSpec("down_proj.weight", (self.hidden, self.inter))]
+        if self.bias:
+            specs += [WeightSpec("gate_proj.bias", (self.inter,), "vector"), WeightSpec("up_proj.bias", (self.inter,), "vector"),
+                      WeightSpec("down_proj.bias", (self.hidden,), "vector")]
+        return specs
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        w = torch.cat([t["gate_proj.weight"], t["up_proj.weight"]], dim=0)
+        b = torch.cat([t["gate_proj.bias"].float(), t["up_proj.bias"].float()]) if self.bias else None
+        self.gate_up.set(w, b)
+        self.down.set(t["down_proj.weight"], t.get("down_proj.bias"))
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        gu = self.gate_up(x, ctx.ws.rows("gate_up", T, 2 * self.inter, self.dtype))
+        act = ctx.ws.rows("ffn_act", T, self.inter, self.dtype)
+        ops.swiglu(gu, act)
+        return self.down(act, ctx.ws.rows("branch", T, self.hidden, self.dtype))
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

@@ -1,0 +1,120 @@
+"""The engine against the plain implementation under every way of cutting the work:
+whole prompts; most of it in one step and the last 32 tokens one by one; portions of changing
+size down to two tokens; up to four live requests mixed, with so few pages that they are used
+again. In float32 and in bfloat16, on tiny configurations that differ in every size and option."""
+import pytest
+import torch
+
+from replay_util import TOL, build_engine, first_bad_row, plain_logits, rel_err, run_cut, run_schedule
+from tiny_configs import TINY, make_weights, random_ids
+
+pytestmark = pytest.mark.gpu
+
+CASES = [("a", 0), ("b", 1), ("c", 2)]
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"a": [5, 17, 33, 100], "b": [3, 40, 70, 100, 200], "c": [2, 31, 64, 129]}
+
+
+def _setup(name, seed):
+    raw = TINY[name]()
+    return raw, make_weights(raw, seed)
+
+
+def _check(got, ref, dtype, what):
+    err = rel_err(got, ref)
+    bad = first_bad_row(got, ref, TOL[dtype])
+    assert bad is None, f"{what}: first wrong position {bad} of {got.shape[0]}, rel err {err:.3e} > {TOL[dtype]:.1e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_whole_prompts(cuda_device, name, seed, dtype):
+    raw, w = _setup(name, seed)
+    eng = build_engine(raw, w, dtype)
+    for n in LENGTHS[name]:
+        ids = random_ids(n, raw["vocab_size"], 100 + n)
+        got = run_cut(eng, ids, [n])
+        _check(got, plain_logits(raw, w, ids, dtype), dtype, f"{name} whole prompt of {n}")
+    eng.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_last_32_one_by_one(cuda_device, name, seed, dtype):
+    raw, w = _setup(name, seed)
+    eng = build_engine(raw, w, dtype)
+    n = LENGTHS[name][-1]
+    ids = random_ids(n, raw["vocab_size"], 7)
+    got = run_cut(eng, ids, [n - 32] + [1] * 32)
+    ref = plain_logits(raw, w, ids, dtype)
+    _check(got, ref, dtype, f"{name} prompt {n - 32} then 32 single tokens")
+    whole = run_cut(eng, ids, [n])
+    # decoding against prefill of the same engine: the same up to rounding
+    assert rel_err(got, whole) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_changing_portions(cuda_device, name, seed, dtype):
+    raw, w = _setup(name, seed)
+    eng = build_engine(raw, w, dtype)
+    n = LENGTHS[name][-1]
+    ids = random_ids(n, raw["vocab_size"], 11)
+    pattern = [16, 7, 2, 5, 3, 17, 2, 1, 31, 2, 9]
+    cuts, left, i = [], n, 0
+    while left > 0:
+        c = min(pattern[i % len(pattern)], left)
+        cuts.append(c)
+        left -= c
+        i += 1
+    got = run_cut(eng, ids, cuts)
+    _check(got, plain_logits(raw, w, ids, dtype), dtype, f"{name} portions {cuts[:8]}...")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_mixed_requests_pages_reused(cuda_device, name, seed, dtype):
+    """Four live requests at most, portions of some beside single tokens of others, and a pool so
+    small that pages of finished requests are handed out again (they are not cleared)."""
+    raw, w = _setup(name, seed)
+    V = raw["vocab_size"]
+    lens = {"p": 3, "q": 40, "r": 70, "s": 100, "t": 55, "u": 90}
+    reqs = {k: random_ids(n, V, 50 + i) for i, (k, n) in enumerate(lens.items())}
+    sched = [
+        [("p", 3), ("q", 16)],
+        [("q", 16), ("r", 16), ("s", 2)],
+        [("q", 7), ("r", 16), ("s", 16)],                       # q: 39 done
+        [("q", 1), ("r", 1), ("s", 16), ("t", 16)],              # q ends; t starts beside decodes
+        [("r", 1), ("s", 30), ("t", 1), ("u", 5)],
+        [("r", 36), ("s", 1), ("t", 2), ("u", 1)],               # r ends (16+16+1+1+36 = 70)
+        [("s", 35), ("t", 36), ("u", 20)],                       # s: 100 done; t: 55 done
+        [("u", 1)], [("u", 1)], [("u", 30)], [("u", 32)],
+    ]
+    # pages of 16: at most 14 are held at once, 26 are allocated over the run: a pool of 16 forces reuse
+    eng = build_engine(raw, w, dtype, num_pages=16)
+    got = run_schedule(eng, reqs, sched)
+    for k, ids in reqs.items():
+        _check(got[k], plain_logits(raw, w, ids, dtype), dtype, f"{name} mixed request {k}")
+    assert not eng.cache.live
+    assert eng.cache.free_pages() == {0: 16}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(cuda_device, dtype):
+    """A short prompt and then many single tokens, crossing LongRoPE's original maximum and many pages."""
+    raw, w = _setup("b", 5)
+    eng = build_engine(raw, w, dtype)
+    ids = random_ids(250, raw["vocab_size"], 3)
+    got = run_cut(eng, ids, [4] + [1] * 246)
+    _check(got, plain_logits(raw, w, ids, dtype), dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens(cuda_device, dtype):
+    """The first tokens of a sequence: a single token, and two."""
+    raw, w = _setup("a", 9)
+    eng = build_engine(raw, w, dtype)
+    for n in (1, 2):
+        ids = random_ids(n, raw["vocab_size"], 40 + n)
+        _check(run_cut(eng, ids, [n]), plain_logits(raw, w, ids, dtype), dtype, f"first {n} token(s)")
+        _check(run_cut(eng, ids, [1] * n), plain_logits(raw, w, ids, dtype), dtype, f"first {n} token(s) one by one")
