@@ -85,5 +85,9 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         return self.runner.step(entries)
 
+    def enable_graphs(self) -> None:
+        """Replay decode-only steps as CUDA graphs from now on."""
+        self.runner.use_graphs = True
+
     def synchronize(self) -> None:
         torch.cuda.current_stream(self.device).synchronize()

@@ -197,3 +197,30 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float =
                                         _c_int, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _ptr(bias), alpha, M, N, K,
              _stream()), "gemm_f32")
+
+
+_ones_k = {}
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], uniform: Optional[torch.Tensor], out: torch.Tensor, greedy: bool = False) -> None:
+    """One token per row of float32 logits [R,V]; per-row temperature, top_k, top_p, uniform number.
+    `greedy`: argmax of every row (no parameters needed)."""
+    _need_cuda(logits, temperature, top_k, top_p, uniform, out)
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32 or out.numel() < R:
+        raise KernelError("sample: logits float32 [R,V] with contiguous rows, out int32 [R]")
+    if greedy:
+        key = (logits.device, R)
+        if key not in _ones_k:
+            _ones_k[key] = torch.ones(max(R, 64), dtype=torch.int32, device=logits.device)
+        top_k, temperature, top_p, uniform = _ones_k[key], None, None, None
+    else:
+        for nm, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                          ("top_p", top_p, torch.float32), ("uniform", uniform, torch.float32)):
+            if t is None or t.dtype != dt or t.numel() < R or not t.is_contiguous():
+                raise KernelError(f"sample: {nm} must be a contiguous {dt} tensor of R entries")
+    f = _fn("sampling", "il_sample", [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                      _c_void_p, _c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
+             _ptr(out), _stream()), "sample")
