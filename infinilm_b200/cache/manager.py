@@ -144,7 +144,8 @@ class CacheManager:
             n = grp.need
             for i in grp.entries:
                 if n.kind == "paged_kv":
-                    shape = (grp.pool.n_pages, 2, n.n_kv_heads, self.page_size, n.head_dim)
+                    # one page more than the pool hands out: padding rows of a replayed step write there
+                    shape = (grp.pool.n_pages + 1, 2, n.n_kv_heads, self.page_size, n.head_dim)
                     dt = self.dtype
                 else:
                     shape = (self.slots.n_slots,) + tuple(n.shape)

@@ -20,6 +20,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager, OutOfPages, PagedKVView, SequenceCache, StateView
 from ..models.causal_lm import CausalLM
 
@@ -44,12 +45,18 @@ class Workspace:
     def __init__(self, device, max_tokens: int):
         self.device, self.max_tokens = device, int(max_tokens)
         self._bufs: Dict[tuple, torch.Tensor] = {}
+        self.version = 0                          # bumped when a buffer is replaced (captured graphs go stale)
 
     def rows(self, tag: str, n: int, width: int, dtype: torch.dtype) -> torch.Tensor:
         key = (tag, width, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.shape[0] < n:
-            cap = max(n, self.max_tokens if buf is None else buf.shape[0] * 2)
+            if buf is None:
+                # per-token buffers are made for the largest step; the logits (rows x vocabulary) for 256 rows
+                cap = max(n, min(self.max_tokens, 256) if tag == "logits" else self.max_tokens)
+            else:
+                cap = max(n, buf.shape[0] * 2)
+                self.version += 1
             buf = torch.empty((cap, width), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:n]
@@ -83,6 +90,7 @@ class StepContext:
     max_qlen: int = 0
     max_kvlen: int = 0
     tap: Optional[Callable] = None                # debug hook: tap(name, resid, pending)
+    lengths_are_bounds: bool = False              # h_qlen / h_kvlen are upper bounds (a step replayed as a graph)
 
 
 class StepRunner:
@@ -95,6 +103,9 @@ class StepRunner:
         self.dtype = model.dtype
         self._desc_dev: Optional[torch.Tensor] = None
         self.tap: Optional[Callable] = None
+        self.use_graphs = False
+        self._graphs: Dict[tuple, "_GraphSlot"] = {}
+        self.h2d_bytes = 0
         self.steps_run = 0
         self.tokens_run = 0
 
@@ -153,24 +164,43 @@ class StepRunner:
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         n_decode = sum(1 for e in entries if len(e.tokens) == 1)
         E = len(entries)
-        qstart = [0] * (E + 1)
+        groups = self.cache.groups
+        paged = [g for g, grp in enumerate(groups) if grp.need.kind == "paged_kv"]
+        widths = {g: max(1, max(len(e.seq.tables[g]) for e in entries)) for g in paged}
+
+        # A decode-only step that wants every row can be replayed as a CUDA graph: the batch is
+        # padded to a bucket of entries and of block-table width, so that the captured launches
+        # and the addresses they read stay the same from step to step.
+        graph_key = None
+        Ep, Tp = E, T
+        if (self.use_graphs and self.tap is None and n_decode == E and not self.cache.has_state
+                and all(len(e.want) == 1 for e in entries)):
+            Ep = _bucket(E, _ENTRY_BUCKETS)
+            widths = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
+            Tp = Ep
+            graph_key = (Ep, tuple(sorted(widths.items())))
+        qstart = [0] * (Ep + 1)
         row_of_entry = {}
         for k, i in enumerate(order):
             row_of_entry[i] = k
             qstart[k + 1] = qstart[k] + len(entries[i].tokens)
+        for k in range(E, Ep):
+            qstart[k + 1] = qstart[k] + 1
         want_rows: List[int] = []
         for i, e in enumerate(entries):
             base = qstart[row_of_entry[i]]
             want_rows.extend(base + w for w in e.want)
+        if graph_key is not None:
+            want_rows = list(range(Ep))           # row k of the logits belongs to sorted entry k
         n_want = len(want_rows)
 
-        groups = self.cache.groups
-        paged = [g for g, grp in enumerate(groups) if grp.need.kind == "paged_kv"]
-        widths = {}
-        for g in paged:
-            widths[g] = max(1, max(len(e.seq.tables[g]) for e in entries))
-        n_ints = 3 * T + (E + 1) + E + max(n_want, 1) + 2 * E + sum(E * w for w in widths.values())
+        n_ints = 3 * Tp + (Ep + 1) + Ep + max(n_want, 1) + 2 * Ep + sum(Ep * w for w in widths.values())
         host, dev = self._desc(n_ints)
+        if graph_key is not None:
+            gs = self._graphs.get(graph_key)
+            if gs is None:
+                gs = self._graphs[graph_key] = _GraphSlot(torch.empty(n_ints, dtype=torch.int32, device=self.device))
+            dev = gs.desc
         h = host.numpy()
         off = 0
 
@@ -179,9 +209,9 @@ class StepRunner:
             v = (off, off + n)
             off += n
             return v
-        s_tok, s_pos, s_ent = take(T), take(T), take(T)
-        s_qs, s_kv, s_want, s_rs, s_wsl = take(E + 1), take(E), take(max(n_want, 1)), take(E), take(E)
-        s_bt = {g: take(E * widths[g]) for g in paged}
+        s_tok, s_pos, s_ent = take(Tp), take(Tp), take(Tp)
+        s_qs, s_kv, s_want, s_rs, s_wsl = take(Ep + 1), take(Ep), take(max(n_want, 1)), take(Ep), take(Ep)
+        s_bt = {g: take(Ep * widths[g]) for g in paged}
         h_qlen, h_kvlen = [], []
         for k, i in enumerate(order):
             e = entries[i]
@@ -201,6 +231,21 @@ class StepRunner:
                 row = h[s_bt[g][0] + k * w: s_bt[g][0] + (k + 1) * w]
                 row[:len(tbl)] = tbl
                 row[len(tbl):] = -1
+        for k in range(E, Ep):                    # padding rows: one token at position 0 of the scratch page
+            a = qstart[k]
+            h[s_tok[0] + a] = 0
+            h[s_pos[0] + a] = 0
+            h[s_ent[0] + a] = k
+            h[s_kv[0] + k] = 1
+            h[s_rs[0] + k] = 0
+            h[s_wsl[0] + k] = 0
+            h_qlen.append(1)
+            h_kvlen.append(1)
+            for g in paged:
+                w = widths[g]
+                row = h[s_bt[g][0] + k * w: s_bt[g][0] + (k + 1) * w]
+                row[:] = -1
+                row[0] = groups[g].pool.n_pages    # the scratch page behind the pool
         h[s_qs[0]: s_qs[1]] = qstart
         if n_want:
             h[s_want[0]: s_want[0] + n_want] = want_rows
@@ -208,14 +253,19 @@ class StepRunner:
         ev = torch.cuda.Event()
         ev.record()
         self._desc_events[self._desc_i] = ev
+        self.h2d_bytes += 4 * off
 
         def view(s):
             return dev[s[0]: s[1]]
+        if graph_key is not None:                 # launch plans must not depend on this step's lengths
+            bound = min(widths[g] for g in paged) * self.cache.page_size if paged else 1
+            h_kvlen, h_qlen = [bound] * Ep, [1] * Ep
         ctx = StepContext(
-            dtype=self.dtype, T=T, n_entries=E, n_decode=n_decode, token_ids=view(s_tok), tok_pos=view(s_pos),
-            tok_entry=view(s_ent), entry_qstart=view(s_qs), entry_kvlen=view(s_kv),
-            want_rows=dev[s_want[0]: s_want[0] + n_want], n_want=n_want, ws=self.ws,
-            h_qlen=h_qlen, h_kvlen=h_kvlen, max_qlen=max(h_qlen), max_kvlen=max(h_kvlen), tap=self.tap)
+            dtype=self.dtype, T=Tp, n_entries=Ep, n_decode=Ep if graph_key is not None else n_decode,
+            token_ids=view(s_tok), tok_pos=view(s_pos), tok_entry=view(s_ent), entry_qstart=view(s_qs),
+            entry_kvlen=view(s_kv), want_rows=dev[s_want[0]: s_want[0] + n_want], n_want=n_want, ws=self.ws,
+            h_qlen=h_qlen, h_kvlen=h_kvlen, max_qlen=max(h_qlen), max_kvlen=max(h_kvlen), tap=self.tap,
+            lengths_are_bounds=graph_key is not None)
 
         caches = []
         for i, st in enumerate(self.model.order):
@@ -226,14 +276,67 @@ class StepRunner:
                 continue
             grp = groups[g]
             if grp.need.kind == "paged_kv":
-                caches.append(PagedKVView(grp.storage[owner], view(s_bt[g]).view(E, widths[g]), self.cache.page_size,
+                caches.append(PagedKVView(grp.storage[owner], view(s_bt[g]).view(Ep, widths[g]), self.cache.page_size,
                                           writable=(owner == i), max_pages=widths[g]))
             else:
                 caches.append(StateView(grp.storage[owner], view(s_rs), view(s_wsl), writable=(owner == i)))
 
-        logits = self.model.forward(ctx, caches)
+        if graph_key is None:
+            logits = self.model.forward(ctx, caches)
+        else:
+            gs = self._graphs[graph_key]
+            if gs.graph is None:
+                if gs.warm < 1:                   # first time eagerly: buffers get allocated, libraries initialised
+                    logits = self.model.forward(ctx, caches)
+                    gs.warm += 1
+                    gs.logits = logits
+                else:
+                    n0 = ops.launch_count()
+                    g_ = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g_):
+                        gs.logits = self.model.forward(ctx, caches)
+                    gs.n_kernels = ops.launch_count() - n0
+                    ops.count_launches(-gs.n_kernels)    # capturing launches nothing
+                    gs.graph = g_
+                    gs.ws_version = self.ws.version
+            if gs.graph is not None:
+                if gs.ws_version != self.ws.version:
+                    raise RuntimeError("a workspace buffer moved after a CUDA graph was captured")
+                gs.graph.replay()
+                ops.count_launches(gs.n_kernels)
+            logits = gs.logits
+            # rows of the logits follow the sorted entries; give them back in the caller's order
+            if any(row_of_entry[i] != i for i in range(E)):
+                idx = torch.tensor([row_of_entry[i] for i in range(E)], device=self.device)
+                logits = logits.index_select(0, idx)
+            else:
+                logits = logits[:E]
         for e in entries:
             self.cache.commit(e.seq, e.seq.length + len(e.tokens))
         self.steps_run += 1
         self.tokens_run += T
         return logits
+
+
+_ENTRY_BUCKETS = [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512]
+
+
+def _bucket(n: int, buckets) -> int:
+    for b in buckets:
+        if n <= b:
+            return b
+    return ((n + 127) // 128) * 128
+
+
+def _bucket_pow2(n: int, lo: int) -> int:
+    b = lo
+    while b < n:
+        b *= 2
+    return b
+
+
+class _GraphSlot:
+    """One captured decode step: its descriptor buffer, its graph and where its logits land."""
+
+    def __init__(self, desc: torch.Tensor):
+        self.desc, self.graph, self.logits, self.warm, self.n_kernels, self.ws_version = desc, None, None, 0, 0, -1

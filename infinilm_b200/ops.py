@@ -52,8 +52,23 @@ def _contig(name: str, t: torch.Tensor) -> None:
         raise KernelError(f"{name} must be contiguous")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (replayed graph nodes included)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
     if code == 0:
+        _launches += 1
         return
     if code == -1:
         raise KernelError(f"{what}: bad argument")
