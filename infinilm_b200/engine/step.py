@@ -65,6 +65,8 @@ class Workspace:
         key = (tag, "flat", dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < n:
+            if buf is not None:
+                self.version += 1
             buf = torch.empty(max(n, 1024), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:n]
@@ -285,6 +287,8 @@ class StepRunner:
             logits = self.model.forward(ctx, caches)
         else:
             gs = self._graphs[graph_key]
+            if gs.graph is not None and gs.ws_version != self.ws.version:
+                gs.graph, gs.warm = None, 0       # a workspace buffer moved: capture again
             if gs.graph is None:
                 if gs.warm < 1:                   # first time eagerly: buffers get allocated, libraries initialised
                     logits = self.model.forward(ctx, caches)
@@ -300,8 +304,6 @@ class StepRunner:
                     gs.graph = g_
                     gs.ws_version = self.ws.version
             if gs.graph is not None:
-                if gs.ws_version != self.ws.version:
-                    raise RuntimeError("a workspace buffer moved after a CUDA graph was captured")
                 gs.graph.replay()
                 ops.count_launches(gs.n_kernels)
             logits = gs.logits

@@ -239,3 +239,49 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Opt
                                       _c_void_p, _c_void_p])
     _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
              _ptr(out), _stream()), "sample")
+
+
+def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                     entry_kvlen: torch.Tensor, n_decode: int, page_size: int, n_heads: int, n_kv_heads: int,
+                     head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
+                     o_part: torch.Tensor, ml_part: torch.Tensor) -> None:
+    """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each).
+    Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
+    _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part)
+    if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: bfloat16 tensors")
+    if o_part.dtype != torch.float32 or ml_part.dtype != torch.float32:
+        raise KernelError("attention_decode: scratch must be float32")
+    need = n_decode * n_heads * n_splits
+    if o_part.numel() < need * head_dim or ml_part.numel() < need * 2:
+        raise KernelError("attention_decode: scratch too small")
+    if out.shape[1] != n_heads * head_dim or out.shape[0] < n_decode or qkv.shape[0] < n_decode:
+        raise KernelError("attention_decode: out [rows, heads*head_dim]")
+    _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
+    f = _fn("attn_decode", "il_attn_decode", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
+                                              _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void_p,
+                                              _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+    _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
+             page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
+             _ptr(o_part), _ptr(ml_part), _stream()), "attention_decode")
+    count_launches(1)                             # the merge kernel
+
+
+def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                      entry_qstart: torch.Tensor, entry_kvlen: torch.Tensor, first_entry: int, n_entries: int,
+                      n_tiles_total: int, page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                      window: Optional[int]) -> None:
+    """bfloat16 causal attention of the tokens of entries [first_entry, n_entries) over their cache pages.
+    n_tiles_total = sum over those entries of ceil(q_len / (64 // (heads/kv_heads)))."""
+    _need_cuda(qkv, out, cache, block_table, entry_qstart, entry_kvlen)
+    if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill: bfloat16 tensors")
+    if out.shape != (qkv.shape[0], n_heads * head_dim):
+        raise KernelError("attention_prefill: out [T, heads*head_dim]")
+    _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
+    f = _fn("attn_prefill", "il_attn_prefill", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                                                _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                                _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
+    _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_qstart),
+             _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads, head_dim, scale,
+             int(window or 0), _stream()), "attention_prefill")

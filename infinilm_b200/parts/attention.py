@@ -33,6 +33,7 @@ class Attention(Mixer):
             raise ValueError(f"attention: head_dim {self.hd} is not supported (multiples of 16 from 16 to 256)")
         self.qkv_bias, self.out_bias = bool(p.get("qkv_bias", False)), bool(p.get("out_bias", False))
         self.window: Optional[int] = p.get("window")
+        self.force_plain = bool(p.get("plain_kernel", False))
         self.scale = 1.0 / math.sqrt(self.hd)
         self.n_qkv = (self.nh + 2 * self.nkv) * self.hd
         self.qkv = Linear(self.hidden, self.n_qkv, dtype)
@@ -76,9 +77,39 @@ class Attention(Mixer):
         self.attend(qkv, out, ctx, cache)
         return self.o_proj(out, ctx.ws.rows("branch", T, self.hidden, self.dtype))
 
+    # The fast bfloat16 kernels take pages of 16 keys and at most 64 query heads per kv head; anything
+    # else, and the whole float32 path, runs the plain kernel.
+    FAST_PAGE = 16
+    FAST_MAX_GROUP = 64
+    TARGET_BLOCKS = 2 * 148                       # decode splits aim at about two blocks per SM
+
     def attend(self, qkv, out, ctx, cache) -> None:
-        ops.attention_plain(qkv, out, cache.storage, cache.block_table, ctx.tok_pos, ctx.tok_entry,
-                            cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window)
+        G = self.nh // self.nkv
+        if (self.dtype != torch.bfloat16 or cache.page_size != self.FAST_PAGE or G > self.FAST_MAX_GROUP
+                or self.force_plain):
+            ops.attention_plain(qkv, out, cache.storage, cache.block_table, ctx.tok_pos, ctx.tok_entry,
+                                cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window)
+            return
+        n_dec, E = ctx.n_decode, ctx.n_entries
+        if n_dec > 0:
+            max_len = max(ctx.h_kvlen[:n_dec])
+            if self.window is not None:
+                max_len = min(max_len, self.window + self.FAST_PAGE)
+            max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.window is not None else 0)
+            base = n_dec * self.nkv * ((G + 15) // 16)
+            n_splits = max(1, min((self.TARGET_BLOCKS + base - 1) // base, (max_pages + 3) // 4))
+            pps = (max_pages + n_splits - 1) // n_splits
+            n_splits = (max_pages + pps - 1) // pps
+            rows = n_dec * self.nh * n_splits
+            ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
+                                 self.nh, self.nkv, self.hd, self.scale, self.window, pps, n_splits,
+                                 ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
+                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32))
+        if E > n_dec:
+            tpt = max(1, 64 // G)
+            n_tiles = sum((q + tpt - 1) // tpt for q in ctx.h_qlen[n_dec:])
+            ops.attention_prefill(qkv, out, cache.storage, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
+                                  n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window)
 
 
 register_part("mixer", "attention", Attention)

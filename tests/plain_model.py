@@ -209,10 +209,7 @@ def sample_plain(logits: torch.Tensor, temperature: float, top_k: int, top_p: fl
     pk = torch.where(keep, p, torch.zeros_like(p))
     target = u * pk.sum()
     cum = torch.cumsum(pk, 0)
-    idx = int((cum <= target).sum().item())
-    while idx >= V or not keep[idx]:
-        idx = idx - 1 if idx >= V else idx + 1
-        if idx >= V:
-            idx = int(torch.nonzero(keep)[-1].item())
-            break
-    return idx
+    hit = torch.nonzero(keep & (cum > target))
+    if hit.numel() == 0:                          # u so close to 1 that rounding leaves nothing: the mode
+        return int(torch.argmax(logits).item())
+    return int(hit[0].item())

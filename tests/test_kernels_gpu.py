@@ -1,0 +1,290 @@
+"""Each kernel alone against a plain float32 reference in torch, at sizes other than the engine's:
+head sizes in steps of 16, odd numbers of heads and groups, widths and vocabularies that are no
+power of two, and inputs built so that a fault shows (one far key that dominates, a window's
+edge, a page's edge)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from infinilm_b200 import ops  # noqa: E402
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+def close(got, ref, dtype, scale=None):
+    got, ref = got.float(), ref.float()
+    denom = ref.abs().max().clamp_min(1e-6) if scale is None else scale
+    err = float((got - ref).abs().max() / denom)
+    assert math.isfinite(err) and err <= TOL[dtype], f"rel err {err:.3e} > {TOL[dtype]:.1e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,H,V", [(1, 64, 97), (37, 200, 331), (5, 4096, 1000)])
+def test_embedding(cuda_device, dtype, T, H, V):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.randn(V, H, device="cuda", generator=g).to(DT[dtype])
+    ids = torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32)
+    out = torch.empty(T, H, device="cuda")
+    ops.embed(ids, table, 12.5, out, round_bf16=(dtype == "bfloat16"))
+    ref = table.float()[ids.long()] * 12.5
+    if dtype == "bfloat16":
+        ref = ref.bfloat16().float()
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,H", [(1, 64), (33, 200), (7, 4096), (3, 5120 + 16)])
+def test_add_rmsnorm(cuda_device, dtype, T, H):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    resid = torch.randn(T, H, device="cuda", generator=g) * 3
+    branch = torch.randn(T, H, device="cuda", generator=g).to(DT[dtype])
+    w32 = 1 + 0.1 * torch.randn(H, device="cuda", generator=g)
+    for w in (w32, w32.bfloat16()):
+        r = resid.clone()
+        out = torch.empty(T, H, device="cuda", dtype=DT[dtype])
+        ops.add_rmsnorm(r, branch, 0.37, w, 1e-5, out)
+        x = resid + 0.37 * branch.float()
+        ref = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+        assert torch.allclose(r, x, rtol=0, atol=1e-6)
+        close(out, ref, dtype)
+    # without a branch, and on chosen rows only (the residual stays as it is)
+    r = resid.clone()
+    rows = torch.tensor([T - 1, 0], device="cuda", dtype=torch.int32)
+    out = torch.empty(2, H, device="cuda", dtype=DT[dtype])
+    ops.add_rmsnorm(r, branch, 2.0, w32, 1e-6, out, rows)
+    x = (resid + 2.0 * branch.float())[rows.long()]
+    close(out, x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w32, dtype)
+    assert torch.equal(r, resid)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu_and_bias(cuda_device, dtype):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    gu = (torch.randn(19, 2 * 264, device="cuda", generator=g) * 4).to(DT[dtype])
+    out = torch.empty(19, 264, device="cuda", dtype=DT[dtype])
+    ops.swiglu(gu, out)
+    a, b = gu.float()[:, :264], gu.float()[:, 264:]
+    close(out, torch.nn.functional.silu(a) * b, dtype)
+    y = torch.randn(19, 331, device="cuda", generator=g).to(DT[dtype])
+    bias = torch.randn(331, device="cuda", generator=g)
+    ref = y.float() + bias
+    ops.add_bias(y, bias)
+    close(y, ref, dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 97, 64), (5, 331, 200), (16, 256, 264), (17, 300, 48), (64, 129, 1000), (200, 513, 333)])
+def test_gemm_f32(cuda_device, M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(M, K, device="cuda", generator=g)
+    w = torch.randn(N, K, device="cuda", generator=g)
+    b = torch.randn(N, device="cuda", generator=g)
+    out = torch.empty(M, N, device="cuda")
+    ops.gemm_f32(a, w, out, 0.7, b)
+    ref = 0.7 * (a.double() @ w.double().t()) + b.double()
+    close(out, ref.float(), "float32")
+    # a row's result is bit-identical whatever the batch around it (another tile shape)
+    out1 = torch.empty(1, N, device="cuda")
+    ops.gemm_f32(a[M - 1:M].contiguous(), w, out1, 0.7, b)
+    assert torch.equal(out1[0], out[M - 1])
+
+
+# -- rope + cache write --------------------------------------------------------------------------
+def _paged_setup(E, lens, nkv, hd, page, dtype, seed, n_extra_pages=3):
+    """Random block tables over shuffled pages for entries with the given kv lengths."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages_each = [(n + page - 1) // page for n in lens]
+    total = sum(n_pages_each) + n_extra_pages
+    perm = torch.randperm(total, generator=g).tolist()
+    W = max(n_pages_each)
+    bt = torch.full((E, W), -1, dtype=torch.int32)
+    k = 0
+    for e in range(E):
+        for i in range(n_pages_each[e]):
+            bt[e, i] = perm[k]
+            k += 1
+    cache = torch.zeros(total, 2, nkv, page, hd, dtype=dtype)
+    return bt, cache
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (5, 1, 48, 24), (6, 3, 32, 32), (3, 3, 80, 0)])
+def test_rope_store(cuda_device, dtype, nh, nkv, hd, rot):
+    page = 16
+    starts, qlens = [0, 30, 15], [5, 1, 20]
+    lens = [s + q for s, q in zip(starts, qlens)]
+    bt, cache = _paged_setup(3, lens, nkv, hd, page, DT[dtype], 4)
+    T = sum(qlens)
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(DT[dtype])
+    tok_pos = torch.cat([torch.arange(s, s + q) for s, q in zip(starts, qlens)]).int()
+    tok_entry = torch.cat([torch.full((q,), e) for e, q in enumerate(qlens)]).int()
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(rot // 2, dtype=torch.float64) * 2 / max(rot, 1)))).float() if rot else None
+    mscale = 1.1547
+    d_qkv, d_cache = qkv.cuda(), cache.cuda()
+    ops.rope_store(d_qkv, tok_pos.cuda(), tok_entry.cuda(), bt.cuda(), d_cache, page, nh, nkv, hd, rot,
+                   inv_freq.cuda() if rot else None, mscale)
+    x = qkv.float().view(T, nh + 2 * nkv, hd)
+    ref = x.clone()
+    if rot:
+        ang = tok_pos.float()[:, None] * inv_freq[None]
+        c, s = (torch.cos(ang) * mscale)[:, None], (torch.sin(ang) * mscale)[:, None]
+        x1, x2 = x[:, :nh + nkv, :rot // 2], x[:, :nh + nkv, rot // 2:rot]
+        ref[:, :nh + nkv, :rot // 2] = x1 * c - x2 * s
+        ref[:, :nh + nkv, rot // 2:rot] = x2 * c + x1 * s
+    close(d_qkv.cpu().view(T, -1, hd), ref, dtype)
+    got = d_qkv.cpu().view(T, nh + 2 * nkv, hd)
+    dc = d_cache.cpu()
+    for t in range(T):
+        e, p = int(tok_entry[t]), int(tok_pos[t])
+        pg, off = int(bt[e, p // page]), p % page
+        assert torch.equal(dc[pg, 0, :, off], got[t, nh:nh + nkv]) and torch.equal(dc[pg, 1, :, off], got[t, nh + nkv:])
+    # nothing else was written
+    written = torch.zeros_like(dc, dtype=torch.bool)
+    for t in range(T):
+        e, p = int(tok_entry[t]), int(tok_pos[t])
+        written[int(bt[e, p // page]), :, :, p % page] = True
+    assert float(dc[~written].abs().max()) == 0.0
+
+
+# -- attention -------------------------------------------------------------------------------------
+def _attn_reference(q, kc, bt, entry_of_tok, pos_of_tok, nh, nkv, hd, page, window):
+    """q [T, nh, hd] f32; kc cache f32; returns [T, nh*hd]."""
+    T = q.shape[0]
+    out = torch.zeros(T, nh, hd)
+    G = nh // nkv
+    for t in range(T):
+        e, p = int(entry_of_tok[t]), int(pos_of_tok[t])
+        lo = max(0, p - window + 1) if window else 0
+        idx = torch.arange(lo, p + 1)
+        pages = bt[e, idx // page].long()
+        K = kc[pages, 0, :, idx % page]            # [n, nkv, hd]
+        V = kc[pages, 1, :, idx % page]
+        for j in range(nh):
+            s = (K[:, j // G] @ q[t, j]) / math.sqrt(hd)
+            out[t, j] = torch.softmax(s, 0) @ V[:, j // G]
+    return out.view(T, nh * hd)
+
+
+def _attn_case(dtype, nh, nkv, hd, starts, qlens, window, seed, dominate=False):
+    page = 16
+    E = len(starts)
+    lens = [s + q for s, q in zip(starts, qlens)]
+    bt, cache = _paged_setup(E, lens, nkv, hd, page, DT[dtype], seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    cache.copy_(torch.randn(cache.shape, generator=g).to(DT[dtype]))       # stale pages hold data too
+    T = sum(qlens)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(DT[dtype])
+    tok_pos = torch.cat([torch.arange(s, s + q) for s, q in zip(starts, qlens)]).int()
+    tok_entry = torch.cat([torch.full((q,), e) for e, q in enumerate(qlens)]).int()
+    if dominate:
+        # one far key of each request gets a large score for one head: a kernel that skips or
+        # misplaces it gives a visibly different output
+        for e in range(E):
+            far = 1 if lens[e] > 1 else 0
+            pg, off = int(bt[e, far // page]), far % page
+            t_last = sum(qlens[:e + 1]) - 1
+            qv = qkv[t_last].view(-1, hd)[0].float()
+            cache[pg, 0, 0, off] = (qv / qv.norm() * 30).to(DT[dtype])
+    qstart = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32)
+    kvlen = torch.tensor(lens, dtype=torch.int32)
+    ref = _attn_reference(qkv.float().view(T, -1, hd)[:, :nh], cache.float(), bt, tok_entry, tok_pos, nh, nkv, hd, page, window)
+    return dict(page=page, bt=bt.cuda(), cache=cache.cuda(), qkv=qkv.cuda(), tok_pos=tok_pos.cuda(), tok_entry=tok_entry.cuda(),
+                qstart=qstart.cuda(), kvlen=kvlen.cuda(), ref=ref, T=T, E=E, lens=lens, qlens=qlens)
+
+
+SHAPES = [(4, 2, 16), (6, 3, 32), (5, 1, 48), (32, 2, 128), (3, 3, 64), (40, 2, 80), (8, 8, 256)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd", SHAPES)
+@pytest.mark.parametrize("window", [None, 21])
+def test_attention_plain(cuda_device, dtype, nh, nkv, hd, window):
+    c = _attn_case(dtype, nh, nkv, hd, [0, 47, 16, 3], [33, 1, 17, 2], window, 10, dominate=True)
+    out = torch.empty(c["T"], nh * hd, device="cuda", dtype=DT[dtype])
+    ops.attention_plain(c["qkv"], out, c["cache"], c["bt"], c["tok_pos"], c["tok_entry"], c["page"], nh, nkv, hd,
+                        1 / math.sqrt(hd), window)
+    close(out.cpu(), c["ref"], dtype)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", SHAPES)
+@pytest.mark.parametrize("window", [None, 21])
+def test_attention_prefill_bf16(cuda_device, nh, nkv, hd, window):
+    for starts, qlens in [([0, 47, 16, 3], [33, 2, 17, 2]), ([0], [130]), ([100, 0], [70, 65])]:
+        c = _attn_case("bfloat16", nh, nkv, hd, starts, qlens, window, 11, dominate=True)
+        out = torch.full((c["T"], nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+        tpt = max(1, 64 // (nh // nkv))
+        n_tiles = sum((q + tpt - 1) // tpt for q in qlens)
+        ops.attention_prefill(c["qkv"], out, c["cache"], c["bt"], c["qstart"], c["kvlen"], 0, c["E"], n_tiles, c["page"],
+                              nh, nkv, hd, 1 / math.sqrt(hd), window)
+        close(out.cpu(), c["ref"], "bfloat16")
+
+
+@pytest.mark.parametrize("nh,nkv,hd", SHAPES)
+@pytest.mark.parametrize("window", [None, 40])
+@pytest.mark.parametrize("splits", [1, 3, 7])
+def test_attention_decode_bf16(cuda_device, nh, nkv, hd, window, splits):
+    starts = [0, 15, 16, 200, 63, 64]
+    c = _attn_case("bfloat16", nh, nkv, hd, starts, [1] * len(starts), window, 12, dominate=True)
+    E = c["E"]
+    max_pages = (max(c["lens"]) + 15) // 16
+    pps = (max_pages + splits - 1) // splits
+    n_splits = (max_pages + pps - 1) // pps
+    out = torch.full((E, nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+    o_part = torch.full((E * nh * n_splits * hd,), float("nan"), device="cuda")
+    ml_part = torch.full((E * nh * n_splits * 2,), float("nan"), device="cuda")
+    ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
+                         window, pps, n_splits, o_part, ml_part)
+    close(out.cpu(), c["ref"], "bfloat16")
+
+
+# -- sampling --------------------------------------------------------------------------------------
+def test_argmax_lowest_index_wins(cuda_device):
+    g = torch.Generator(device="cuda").manual_seed(6)
+    logits = torch.randn(9, 73448, device="cuda", generator=g)
+    logits[3, 500] = logits[3, 70000] = 50.0
+    logits[4, 0] = 60.0
+    logits[5, 73447] = 60.0
+    out = torch.empty(9, dtype=torch.int32, device="cuda")
+    ops.sample(logits, None, None, None, None, out, greedy=True)
+    ref = torch.argmax(logits, -1)
+    ref[3] = 500
+    assert out.tolist() == ref.tolist()
+
+
+def test_sampling_matches_plain(cuda_device):
+    import plain_model
+    g = torch.Generator().manual_seed(7)
+    V = 331
+    R = 24
+    logits = (torch.randn(R, V, generator=g) * 3)
+    temps = [0.7, 1.0, 1.3, 0.0] * 6
+    ks = [0, 5, 1, 50, 331, 400] * 4
+    ps = [1.0, 0.8, 0.5, 0.95] * 6
+    us = [float(x) for x in torch.rand(R, generator=g)]
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(logits.cuda(), torch.tensor(temps).cuda(), torch.tensor(ks, dtype=torch.int32).cuda(),
+               torch.tensor(ps).cuda(), torch.tensor(us).cuda(), out)
+    ref = [plain_model.sample_plain(logits[i], temps[i], ks[i], ps[i], us[i]) for i in range(R)]
+    assert out.tolist() == ref
+
+
+def test_sampling_distribution(cuda_device):
+    """Many draws follow softmax(logits / T) restricted to the kept set."""
+    V = 50
+    logits = torch.linspace(-2, 2, V)
+    R = 4000
+    g = torch.Generator().manual_seed(8)
+    us = torch.rand(R, generator=g)
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(logits.repeat(R, 1).cuda(), torch.full((R,), 0.8).cuda(), torch.full((R,), 10, dtype=torch.int32).cuda(),
+               torch.full((R,), 1.0).cuda(), us.cuda(), out)
+    counts = torch.bincount(out.cpu().long(), minlength=V).float() / R
+    p = torch.softmax(logits / 0.8, 0)
+    p[:V - 10] = 0
+    p /= p.sum()
+    assert counts[:V - 10].sum() == 0
+    assert float((counts - p).abs().max()) < 0.03
