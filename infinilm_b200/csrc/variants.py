@@ -3,7 +3,7 @@
 # Kernels specialised by head size are compiled for the sizes listed here ahead of time; any
 # other multiple of 16 up to 256 is compiled the first time a model asks for it.
 PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
-PER_HEAD_DIM = ("attn_decode", "attn_prefill")
+PER_HEAD_DIM = ("attn_decode", "attn_prefill", "attn_decode_noalloc")
 
 
 def all_variants():
