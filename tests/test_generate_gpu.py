@@ -1,0 +1,164 @@
+"""Generation through the Python entry point and the command line tools: greedy against the plain
+implementation, seeded temperature sampling (repeatable, independent of what else is in the
+batch, equal to the plain sampler), CUDA-graph replay against eager steps, preemption by
+recomputation, and `bin/trace_run` as a separate process."""
+import json
+import os
+import struct
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+from replay_util import TOL, plain_logits, rel_err
+from tiny_configs import TINY, make_weights, random_ids, tiny_a, tiny_b
+
+pytestmark = pytest.mark.gpu
+
+from infinilm_b200.config import config_from_json  # noqa: E402
+from infinilm_b200.llm import LLM, SamplingParams  # noqa: E402
+from infinilm_b200.sampling import uniform01  # noqa: E402
+from infinilm_b200.weights import write_model_folder  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_greedy_generation_matches_plain(cuda_device):
+    raw = tiny_a()
+    w = make_weights(raw, 0)
+    prompts = [random_ids(n, raw["vocab_size"], 20 + n) for n in (5, 17, 33)]
+    llm = LLM.from_tensors(config_from_json(raw), w, dtype="float32", num_blocks=16, block_size=16, max_batch_size=3)
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(top_k=1, max_tokens=16, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == plain_model.greedy_generate(raw, w, p, 16)
+        assert o.finished and o.finish_reason.value == "length" and o.prompt_token_ids == p
+    assert llm.stats()["free_pages"] == 16
+    # bfloat16: the same tokens as long as the plain top-2 margin is wide enough to survive rounding
+    llm16 = LLM.from_tensors(config_from_json(raw), w, dtype="bfloat16", num_blocks=16, block_size=16, max_batch_size=3)
+    outs16 = llm16.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(top_k=1, max_tokens=16, ignore_eos=True))
+    for p, o in zip(prompts, outs16):
+        ids = list(p)
+        for t in o.outputs[0].token_ids:
+            lg = plain_logits(raw, w, ids, "bfloat16")[-1]
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) > 4 * TOL["bfloat16"] * float(lg.abs().max()):
+                assert t == int(torch.argmax(lg))
+            ids.append(t)
+
+
+def test_eos_stops_generation(cuda_device):
+    raw = tiny_a()
+    w = make_weights(raw, 0)
+    p = random_ids(9, raw["vocab_size"], 3)
+    ref = plain_model.greedy_generate(raw, w, p, 12)
+    raw2 = dict(raw, eos_token_id=ref[4])
+    first = ref.index(ref[4])
+    llm = LLM.from_tensors(config_from_json(raw2), w, dtype="float32", num_blocks=8, block_size=16, max_batch_size=2)
+    o = llm.generate(prompt_token_ids=[p], sampling_params=SamplingParams(top_k=1, max_tokens=12))[0]
+    assert o.outputs[0].token_ids == ref[:first + 1] and o.finish_reason.value == "eos_token"
+    o = llm.generate(prompt_token_ids=[p], sampling_params=SamplingParams(top_k=1, max_tokens=12, ignore_eos=True))[0]
+    assert o.outputs[0].token_ids == ref
+
+
+def _plain_sampled(raw, w, prompt, n_new, sp, seed, stream):
+    ids, out = list(prompt), []
+    for i in range(n_new):
+        lg = plain_model.forward(raw, w, ids)[-1]
+        t = plain_model.sample_plain(lg, sp.temperature, sp.top_k, sp.top_p, uniform01(seed, stream, i))
+        out.append(t)
+        ids.append(t)
+    return out
+
+
+def test_temperature_sampling_mixed_batch(cuda_device):
+    """Four requests with prompts of 3, 40, 70 and 100 tokens under chunked prefill (portions of 16),
+    temperature 0.7 with a fixed seed: repeatable, the same whether a request runs alone or with the
+    others, and equal to the plain sampler on plain logits."""
+    raw = tiny_b()
+    w = make_weights(raw, 1)
+    cfg = config_from_json(raw)
+    prompts = [random_ids(n, raw["vocab_size"], 30 + n) for n in (3, 40, 70, 100)]
+    sp = SamplingParams(temperature=0.7, top_k=0, top_p=0.9, max_tokens=12, ignore_eos=True)
+
+    def run(batch, **kw):
+        llm = LLM.from_tensors(cfg, w, dtype="float32", num_blocks=40, block_size=16, max_batch_size=4,
+                               chunk_size=16, max_num_batched_tokens=40, seed=5, **kw)
+        return [o.outputs[0].token_ids for o in llm.generate(prompt_token_ids=batch, sampling_params=sp)]
+    together = run(prompts)
+    assert together == run(prompts)
+    assert len({tuple(t) for t in together}) == 4
+    for i, p in enumerate(prompts):
+        # alone, the request is the engine's first (stream 0); give it the stream it had in the batch
+        llm = LLM.from_tensors(cfg, w, dtype="float32", num_blocks=40, block_size=16, max_batch_size=4, chunk_size=16,
+                               max_num_batched_tokens=40, seed=5)
+        llm._n_requests = i
+        assert llm.generate(prompt_token_ids=[p], sampling_params=sp)[0].outputs[0].token_ids == together[i]
+        assert together[i] == _plain_sampled(raw, w, p, 12, sp, 5, i)
+    other = LLM.from_tensors(cfg, w, dtype="float32", num_blocks=40, block_size=16, max_batch_size=4, seed=6)
+    assert [o.outputs[0].token_ids for o in other.generate(prompt_token_ids=prompts, sampling_params=sp)] != together
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_equals_eager(cuda_device, dtype):
+    raw = tiny_b()
+    w = make_weights(raw, 2)
+    cfg = config_from_json(raw)
+    prompts = [random_ids(n, raw["vocab_size"], 60 + n) for n in (7, 30, 18)]
+    sp = SamplingParams(top_k=1, max_tokens=40, ignore_eos=True)
+    outs = []
+    for graph in (False, True):
+        llm = LLM.from_tensors(cfg, w, dtype=dtype, num_blocks=32, block_size=16, max_batch_size=4, enable_graph=graph)
+        outs.append([o.outputs[0].token_ids for o in llm.generate(prompt_token_ids=prompts, sampling_params=sp)])
+        if graph:
+            assert any(g.graph is not None for g in llm.engine.runner._graphs.values())
+    assert outs[0] == outs[1]
+
+
+def test_preemption_recomputes_to_the_same_tokens(cuda_device):
+    """With so few pages that the younger request is preempted and recomputed, greedy outputs are
+    those of a roomy run."""
+    raw = tiny_a()
+    w = make_weights(raw, 3)
+    cfg = config_from_json(raw)
+    prompts = [random_ids(20, raw["vocab_size"], 1), random_ids(20, raw["vocab_size"], 2)]
+    sp = SamplingParams(top_k=1, max_tokens=60, ignore_eos=True)
+    roomy = LLM.from_tensors(cfg, w, dtype="float32", num_blocks=32, block_size=16, max_batch_size=2)
+    ref = [o.outputs[0].token_ids for o in roomy.generate(prompt_token_ids=prompts, sampling_params=sp)]
+    tight = LLM.from_tensors(cfg, w, dtype="float32", num_blocks=8, block_size=16, max_batch_size=2, admission="optimistic")
+    got = [o.outputs[0].token_ids for o in tight.generate(prompt_token_ids=prompts, sampling_params=sp)]
+    assert tight.scheduler.n_preemptions >= 1 and got == ref
+    waits = LLM.from_tensors(cfg, w, dtype="float32", num_blocks=8, block_size=16, max_batch_size=2)   # worst_case
+    assert [o.outputs[0].token_ids for o in waits.generate(prompt_token_ids=prompts, sampling_params=sp)] == ref
+    assert waits.scheduler.n_preemptions == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_as_a_process(cuda_device, tmp_path, dtype):
+    raw = tiny_b()
+    cfg = config_from_json(raw)
+    model_dir = write_model_folder(cfg, 7, str(tmp_path / "model"))
+    from infinilm_b200.weights import random_tensors
+    w = random_tensors(cfg, 7, "cpu")
+    a, b = random_ids(50, raw["vocab_size"], 1), random_ids(21, raw["vocab_size"], 2)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+        {"step": 1, "entries": [{"id": "b", "tokens": b[:2], "want": []}], "end": []},          # nothing wanted: no file
+        {"step": 2, "entries": [{"id": "a", "tokens": a[30:31], "want": [0]}, {"id": "b", "tokens": b[2:21], "want": [18, 0]}], "end": ["b"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[31:50], "want": list(range(19))}], "end": ["a"]},
+    ]
+    out_dir = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+                           "--out", str(out_dir), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
+    assert sorted(os.listdir(out_dir)) == ["0.f32", "2.f32", "3.f32"]
+    V = raw["vocab_size"]
+    la, lb = plain_logits(raw, w, a, dtype), plain_logits(raw, w, b, dtype)
+    want = {0: torch.stack([la[0], la[29]]), 2: torch.stack([la[30], lb[20], lb[2]]), 3: la[31:50]}
+    for s, ref in want.items():
+        got = torch.from_numpy(np.fromfile(out_dir / f"{s}.f32", dtype="<f4").reshape(-1, V))
+        assert rel_err(got, ref) <= TOL[dtype], f"step {s}"
