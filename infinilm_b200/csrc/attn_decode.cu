@@ -157,32 +157,76 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     }
 }
 
-__global__ void attn_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
-                                         const int* __restrict__ entry_kvlen, int nh, int window, int pages_per_split,
-                                         int n_splits, __nv_bfloat16* __restrict__ out) {
-    const int e = blockIdx.y, head = blockIdx.x;
+constexpr int AD_MAX_SPLITS = 128;
+
+// One warp per (token, head): the split factors exp2(m_s - M) are computed once (lanes over splits)
+// and kept in shared memory; then each lane sums four output columns over the splits.
+__global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                                                const int* __restrict__ entry_kvlen, int nh, int n_rows, int window,
+                                                                int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out) {
+    __shared__ float fs[4][AD_MAX_SPLITS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;        // = e * nh + head
+    if (row >= n_rows) return;
+    const int e = row / nh;
     const int kvlen = entry_kvlen[e];
     const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
     const int n_pages = (kvlen - 1) / AD_PAGE - lo / AD_PAGE + 1;
     int n_valid = (n_pages + pages_per_split - 1) / pages_per_split;
     if (n_valid > n_splits) n_valid = n_splits;
-    const size_t pr0 = ((size_t)e * nh + head) * n_splits;
+    const size_t pr0 = (size_t)row * n_splits;
     float M = -INFINITY;
-    for (int s = 0; s < n_valid; ++s) M = fmaxf(M, ml_part[(pr0 + s) * 2]);
+    for (int s = lane; s < n_valid; s += 32) M = fmaxf(M, ml_part[(pr0 + s) * 2]);
+    M = il_warp_max(M);
     float L = 0.f;
-    for (int s = 0; s < n_valid; ++s) {
+    for (int s = lane; s < n_valid; s += 32) {
         const float ms = ml_part[(pr0 + s) * 2];
-        L += (ms == -INFINITY ? 0.f : exp2f(ms - M)) * ml_part[(pr0 + s) * 2 + 1];
+        const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+        fs[warp][s] = f;
+        L += f * ml_part[(pr0 + s) * 2 + 1];
     }
+    L = il_warp_sum(L);
+    __syncwarp();
     const float inv = 1.f / L;
-    for (int d = threadIdx.x; d < AT_HD; d += blockDim.x) {
-        float acc = 0.f;
+    for (int d = lane * 4; d < AT_HD; d += 128) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
         for (int s = 0; s < n_valid; ++s) {
-            const float ms = ml_part[(pr0 + s) * 2];
-            acc += (ms == -INFINITY ? 0.f : exp2f(ms - M)) * o_part[(pr0 + s) * AT_HD + d];
+            const float4 v = *reinterpret_cast<const float4*>(o_part + (pr0 + s) * AT_HD + d);
+            const float f = fs[warp][s];
+            acc.x += f * v.x;
+            acc.y += f * v.y;
+            acc.z += f * v.z;
+            acc.w += f * v.w;
         }
-        out[((size_t)e * nh + head) * AT_HD + d] = __float2bfloat16_rn(acc * inv);
+        const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(out + (size_t)row * AT_HD + d) = make_uint2(a, b);
     }
+}
+
+// Launches both kernels. Scratch: o_part float32 [n_decode*nh*n_splits*head_dim], ml_part [n_decode*nh*n_splits*2].
+static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
+                     const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
+                     int n_splits, float* o_part, float* ml_part, cudaStream_t stream) {
+    static bool attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        attr_set[dev] = true;
+    }
+    const int G = nh / nkv, row_tiles = (G + 15) / 16;
+    dim3 grid(n_splits, nkv * row_tiles, n_decode);
+    attn_decode_kernel<<<grid, AD_WARPS * 32, AD_SMEM, stream>>>(
+        (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
+        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part);
+    IL_LAUNCH_CHECK();
+    const int n_rows = n_decode * nh;
+    attn_decode_merge_kernel<<<(n_rows + 3) / 4, 128, 0, stream>>>(o_part, ml_part, entry_kvlen, nh, n_rows, window, pages_per_split,
+                                                                  n_splits, (__nv_bfloat16*)out);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
 }
 
 // Scratch the caller provides: o_part float32 [n_decode * nh * n_splits * head_dim], ml_part [n_decode * nh * n_splits * 2].
@@ -193,21 +237,7 @@ IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const v
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split <= 0 || n_splits <= 0) return IL_BAD_ARG;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
-        if (e != cudaSuccess) return 1000 + (int)e;
-        attr_set = true;
-    }
-    const int G = nh / nkv, row_tiles = (G + 15) / 16;
-    dim3 grid(n_splits, nkv * row_tiles, n_decode);
-    attn_decode_kernel<<<grid, AD_WARPS * 32, AD_SMEM, stream>>>(
-        (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
-        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part);
-    IL_LAUNCH_CHECK();
-    dim3 mgrid(nh, n_decode);
-    attn_decode_merge_kernel<<<mgrid, HEAD_DIM <= 64 ? 32 : 64, 0, stream>>>(o_part, ml_part, entry_kvlen, nh, window, pages_per_split,
-                                                                           n_splits, (__nv_bfloat16*)out);
-    IL_LAUNCH_CHECK();
-    return IL_OK;
+    if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
+    return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
+                     pages_per_split, n_splits, o_part, ml_part, stream);
 }

@@ -9,7 +9,6 @@ static __device__ __align__(256) float il_noalloc_scratch[(size_t)IL_NOALLOC_MAX
 
 #define IL_NOALLOC_MAX_DEVICES 64
 static float* il_noalloc_addr[IL_NOALLOC_MAX_DEVICES];    // device address of the array, per device (0: not looked up)
-static bool il_noalloc_attr[IL_NOALLOC_MAX_DEVICES];
 
 extern "C" __attribute__((visibility("default")))
 int il_attn_decode_noalloc(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
@@ -20,6 +19,7 @@ int il_attn_decode_noalloc(const void* qkv, int row_stride, void* out, const voi
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split <= 0 || n_splits <= 0) return IL_BAD_ARG;
     const long long rows = (long long)n_decode * nh * n_splits;
     if (rows > IL_NOALLOC_MAX_ROWS) return IL_NOALLOC_TOO_LARGE;
+    if (n_splits > AD_MAX_SPLITS) return IL_NOALLOC_TOO_LARGE;
 
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= IL_NOALLOC_MAX_DEVICES) return IL_NOALLOC_NO_SYMBOL;
@@ -30,25 +30,10 @@ int il_attn_decode_noalloc(const void* qkv, int row_stride, void* out, const voi
         if (cudaGetSymbolAddress((void**)&p, il_noalloc_scratch) != cudaSuccess || !p) return IL_NOALLOC_NO_SYMBOL;
         il_noalloc_addr[dev] = p;
     }
-    if (!il_noalloc_attr[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
-        if (e != cudaSuccess) return 1000 + (int)e;
-        il_noalloc_attr[dev] = true;
-    }
     float* o_part = il_noalloc_addr[dev];
     float* ml_part = o_part + (size_t)IL_NOALLOC_MAX_ROWS * HEAD_DIM;
-
-    const int G = nh / nkv, row_tiles = (G + 15) / 16;
-    dim3 grid(n_splits, nkv * row_tiles, n_decode);
-    attn_decode_kernel<<<grid, AD_WARPS * 32, AD_SMEM, stream>>>(
-        (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
-        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part);
-    IL_LAUNCH_CHECK();
-    dim3 mgrid(nh, n_decode);
-    attn_decode_merge_kernel<<<mgrid, HEAD_DIM <= 64 ? 32 : 64, 0, stream>>>(o_part, ml_part, entry_kvlen, nh, window, pages_per_split,
-                                                                           n_splits, (__nv_bfloat16*)out);
-    IL_LAUNCH_CHECK();
-    return IL_OK;
+    return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
+                     pages_per_split, n_splits, o_part, ml_part, stream);
 }
 
 extern "C" __attribute__((visibility("default")))

@@ -16,6 +16,30 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
     }
 }
 
+// 8 bfloat16 (or 4 float) per thread and access; I must be a multiple of the vector width.
+template <typename TA, int VEC>
+__global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, size_t total_vec) {
+    const int ivec = I / VEC;
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total_vec; idx += stride) {
+        const size_t t = idx / ivec;
+        const int i = (int)(idx - t * ivec) * VEC;
+        const uint4 gq = *reinterpret_cast<const uint4*>(gu + t * 2 * I + i);
+        const uint4 uq = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + i);
+        uint4 oq;
+        const TA* gp = reinterpret_cast<const TA*>(&gq);
+        const TA* up = reinterpret_cast<const TA*>(&uq);
+        TA* op = reinterpret_cast<TA*>(&oq);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            const float g = il_to_f(gp[k]), u = il_to_f(up[k]);
+            op[k] = il_from_f<TA>(g / (1.f + expf(-g)) * u);
+        }
+        *reinterpret_cast<uint4*>(out + t * I + i) = oq;
+    }
+}
+
 template <typename TA>
 __global__ void add_bias_kernel(TA* __restrict__ y, const void* __restrict__ b, int b_kind, int N, size_t total) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -36,6 +60,22 @@ IL_EXPORT int il_swiglu(const void* gu, void* out, int act_kind, int T, int I, c
     if (T <= 0) return IL_OK;
     if (I <= 0) return IL_BAD_ARG;
     const size_t total = (size_t)T * I;
+    if (act_kind == IL_BF16 && I % 8 == 0) {
+        const size_t tv = total / 8;
+        size_t g = (tv + 255) / 256;
+        if (g > 148 * 32) g = 148 * 32;
+        swiglu_vec_kernel<__nv_bfloat16, 8><<<(int)g, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I, tv);
+        IL_LAUNCH_CHECK();
+        return IL_OK;
+    }
+    if (act_kind == IL_F32 && I % 4 == 0) {
+        const size_t tv = total / 4;
+        size_t g = (tv + 255) / 256;
+        if (g > 148 * 32) g = 148 * 32;
+        swiglu_vec_kernel<float, 4><<<(int)g, 256, 0, stream>>>((const float*)gu, (float*)out, I, tv);
+        IL_LAUNCH_CHECK();
+        return IL_OK;
+    }
     const int threads = 256, grid = grid_for(total, threads);
     if (act_kind == IL_F32)
         swiglu_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);

@@ -97,7 +97,7 @@ class Attention(Mixer):
                 max_len = min(max_len, self.window + self.FAST_PAGE)
             max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.window is not None else 0)
             base = n_dec * self.nkv * ((G + 15) // 16)
-            n_splits = max(1, min((self.TARGET_BLOCKS + base - 1) // base, (max_pages + 3) // 4))
+            n_splits = max(1, min((self.TARGET_BLOCKS + base - 1) // base, (max_pages + 3) // 4, 128))
             pps = (max_pages + n_splits - 1) // n_splits
             n_splits = (max_pages + pps - 1) // pps
             rows = n_dec * self.nh * n_splits
