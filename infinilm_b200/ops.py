@@ -285,3 +285,29 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_qstart),
              _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads, head_dim, scale,
              int(window or 0), _stream()), "attention_prefill")
+
+
+SKINNY_MAX_ROWS = 16
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
+                bias: Optional[torch.Tensor] = None, glu: bool = False) -> None:
+    """out[M,N] = alpha * x[M,K] @ w[N,K]^T (+ bias) for M <= 16 bfloat16 rows; out bfloat16 or float32.
+    glu: w is [2N,K] (gate rows, then up rows) and out[M,N] = silu(gate) * up."""
+    _need_cuda(x, w, out, bias)
+    M, K = x.shape
+    N = w.shape[0] // 2 if glu else w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_skinny: bfloat16 x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_skinny: innermost dimension must be contiguous")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.shape[0]):
+        raise KernelError("gemm_skinny: bias float32, one per weight row")
+    f = _fn("gemm_skinny", "il_gemm_skinny", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p,
+                                              _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), kind_of(out.dtype), out.stride(0), _ptr(bias), alpha,
+             M, N, K, int(glu), _stream()), "gemm_skinny")
+
+
+def skinny_ok(M: int, K: int) -> bool:
+    return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0

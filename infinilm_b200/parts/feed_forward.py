@@ -41,6 +41,11 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx):
         T = x.shape[0]
+        if self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden):
+            # decode: gate and up rows streamed together, SiLU(gate)*up in the epilogue
+            act = ctx.ws.rows("ffn_act", T, self.inter, self.dtype)
+            ops.gemm_skinny(x, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=True)
+            return self.down(act, ctx.ws.rows("branch", T, self.hidden, self.dtype))
         gu = self.gate_up(x, ctx.ws.rows("gate_up", T, 2 * self.inter, self.dtype))
         act = ctx.ws.rows("ffn_act", T, self.inter, self.dtype)
         ops.swiglu(gu, act)

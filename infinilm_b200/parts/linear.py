@@ -2,8 +2,9 @@
 
 Parity with InfiniLM: `csrc/layers/linear/base_linear.cpp:35-44` and
 `csrc/layers/quantization/none_quantization.cpp:26-46` (weight [out,in], optional bias, a scale
-`alpha` passed into the product). The float32 path runs the FFMA kernel of this package; the
-bfloat16 path calls the library matrix product, as InfiniLM does for its linears.
+`alpha` passed into the product). The float32 path runs the FFMA kernel of this package. On the
+bfloat16 path up to 16 rows (decode) run this package's weight-streaming kernel; more rows call
+the library matrix product, as InfiniLM does for its linears.
 """
 from __future__ import annotations
 
@@ -32,6 +33,10 @@ class Linear:
         """x [M,in] -> out [M,out]. `out_f32`: out is float32 even on the bfloat16 path."""
         if self.dtype == torch.float32:
             ops.gemm_f32(x, self.weight, out, self.alpha, self.bias)
+            return out
+        if ops.skinny_ok(x.shape[0], self.in_features):
+            # a few rows (decode): the weight-streaming kernel of this package
+            ops.gemm_skinny(x, self.weight, out, self.alpha, self.bias)
             return out
         # Library matrix product (cuBLAS through torch), f32 accumulation inside.
         if out_f32:

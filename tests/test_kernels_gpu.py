@@ -288,3 +288,35 @@ def test_sampling_distribution(cuda_device):
     p /= p.sum()
     assert counts[:V - 10].sum() == 0
     assert float((counts - p).abs().max()) < 0.03
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 97, 64), (8, 331, 200), (3, 4096, 4096), (9, 300, 264), (16, 129, 1000), (5, 16, 8), (12, 5000, 320)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_gemm_skinny(cuda_device, M, N, K, out_dtype):
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=DT[out_dtype])
+    ops.gemm_skinny(x, w, out, 0.7, b)
+    ref = 0.7 * (x.double() @ w.double().t()) + b.double()
+    close(out, ref.float(), "float32" if out_dtype == "float32" else "bfloat16")
+    # a row's bits do not depend on the rows beside it
+    out1 = torch.empty(1, N, device="cuda", dtype=DT[out_dtype])
+    ops.gemm_skinny(x[M - 1:M].contiguous(), w, out1, 0.7, b)
+    assert torch.equal(out1[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 160, 64), (8, 264, 200), (13, 320, 192), (4, 16384, 4096)])
+def test_gemm_skinny_swiglu(cuda_device, M, I, K):
+    g = torch.Generator(device="cuda").manual_seed(10)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * I, K, device="cuda", generator=g) * 2 / math.sqrt(K)).bfloat16()
+    b = torch.randn(2 * I, device="cuda", generator=g) * 0.1
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_skinny(x, w, out, 1.0, b, glu=True)
+    y = x.double() @ w.double().t() + b.double()
+    close(out, (torch.nn.functional.silu(y[:, :I]) * y[:, I:]).float(), "bfloat16")
+    ops.gemm_skinny(x, w, out, 1.0, None, glu=True)
+    y = x.double() @ w.double().t()
+    close(out, (torch.nn.functional.silu(y[:, :I]) * y[:, I:]).float(), "bfloat16")
