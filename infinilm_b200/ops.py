@@ -311,3 +311,33 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: floa
 
 def skinny_ok(M: int, K: int) -> bool:
     return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0
+
+
+_stream_status = {}
+
+
+def stream_status(device) -> torch.Tensor:
+    """The status word of the bulk-copy kernels on `device`: 0, or non-zero after a bounded wait ran out."""
+    key = torch.device(device).index or 0
+    if key not in _stream_status:
+        _stream_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _stream_status[key]
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
+                bias: Optional[torch.Tensor] = None, glu: bool = False) -> None:
+    """The same product as `gemm_skinny`, weights streamed by bulk asynchronous copies (TMA) through
+    a shared-memory ring; one persistent block per SM."""
+    _need_cuda(x, w, out, bias)
+    M, K = x.shape
+    N = w.shape[0] // 2 if glu else w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_stream: bfloat16 x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_stream: innermost dimension must be contiguous")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.shape[0]):
+        raise KernelError("gemm_stream: bias float32, one per weight row")
+    f = _fn("gemm_stream", "il_gemm_stream", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p,
+                                              _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), kind_of(out.dtype), out.stride(0), _ptr(bias), alpha,
+             M, N, K, int(glu), _ptr(stream_status(x.device)), _stream()), "gemm_stream")

@@ -320,3 +320,23 @@ def test_gemm_skinny_swiglu(cuda_device, M, I, K):
     ops.gemm_skinny(x, w, out, 1.0, None, glu=True)
     y = x.double() @ w.double().t()
     close(out, (torch.nn.functional.silu(y[:, :I]) * y[:, I:]).float(), "bfloat16")
+
+
+@pytest.mark.parametrize("M,N,K,glu", [(1, 97, 64, False), (8, 331, 200, False), (3, 4096, 4096, False), (16, 300, 1000, False),
+                                       (8, 264, 200, True), (13, 320, 1032, True)])
+def test_gemm_stream_equals_skinny(cuda_device, M, N, K, glu):
+    """The bulk-copy (TMA ring) variant of the decode product gives the same bits as the register-streaming one."""
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * N if glu else N, K, device="cuda", generator=g) / math.sqrt(K)).bfloat16()
+    b = torch.randn(w.shape[0], device="cuda", generator=g)
+    a = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    c = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_skinny(x, w, a, 0.9, b, glu=glu)
+    ops.gemm_stream(x, w, c, 0.9, b, glu=glu)
+    torch.cuda.synchronize()
+    assert int(ops.stream_status("cuda:0").item()) == 0
+    y = x.double() @ w.double().t() * 0.9 + b.double()
+    ref = (torch.nn.functional.silu(y[:, :N]) * y[:, N:]) if glu else y
+    close(c, ref.float(), "bfloat16")
+    assert torch.equal(a, c)
