@@ -15,7 +15,7 @@
 
 constexpr int AD_WARPS = 4;
 constexpr int AD_PAGE = 16;                       // keys per tile = page size this kernel takes
-constexpr int AD_STAGES = (HEAD_DIM <= 128) ? 4 : 2;
+constexpr int AD_STAGES = (HEAD_DIM <= 128) ? 3 : 2;      // 4 warps x 3 stages of a page: two blocks fit on an SM at head_dim 128
 constexpr int AD_STAGE_BYTES = 2 * AD_PAGE * AT_ROW_BYTES;
 constexpr int AD_SMEM_PIPE = AD_WARPS * AD_STAGES * AD_STAGE_BYTES;
 constexpr int AD_SMEM_MERGE = AD_WARPS * 16 * (HEAD_DIM + 2) * 4;

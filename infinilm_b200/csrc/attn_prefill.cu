@@ -32,7 +32,9 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // which entry and which tokens
-    int tile = blockIdx.x, e = first_entry;
+    // Tiles are taken from the last to the first: the last tokens of a prompt have the most keys to
+    // visit, and starting the longest blocks first shortens the tail of the launch.
+    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, e = first_entry;
     for (; e < n_entries; ++e) {
         const int nt = (entry_qstart[e + 1] - entry_qstart[e] + tpt - 1) / tpt;
         if (tile < nt) break;
@@ -123,8 +125,31 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
         for (int p = 0; p < AP_TILE_PAGES; ++p) {
             const int k0 = key_base + p * AP_PAGE;
             use[p] = (k0 <= wmax) && (k0 + AP_PAGE - 1 >= wmin_lo);   // the same for the whole warp
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s[p][nt][j] = 0.f;
+        }
+        // S = Q.K^T for the four pages together: eight independent accumulator chains per k-step
+        {
+            const int mat = lane >> 3, rr = lane & 7;
+            const uint32_t kb = st + ((mat >> 1) * 8 + rr) * AT_ROW_BYTES + (mat & 1) * 16;
+#pragma unroll
+            for (int kk = 0; kk < AT_KSTEPS; ++kk) {
+#pragma unroll
+                for (int p = 0; p < AP_TILE_PAGES; ++p) {
+                    if (!use[p]) continue;
+                    uint32_t b0, b1, b2, b3;
+                    at_ldmatrix_x4(b0, b1, b2, b3, kb + p * AP_PAGE_BYTES + kk * 32);
+                    at_mma(s[p][0], qf[kk], b0, b1);
+                    at_mma(s[p][1], qf[kk], b2, b3);
+                }
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < AP_TILE_PAGES; ++p) {
             if (!use[p]) continue;
-            at_qk_16keys(s[p], qf, st + p * AP_PAGE_BYTES, lane);
+            const int k0 = key_base + p * AP_PAGE;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll

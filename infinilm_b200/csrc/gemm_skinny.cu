@@ -1,8 +1,8 @@
 // Matrix product for a few activation rows (decode): out[M,N] = alpha * x[M,K] . W[N,K]^T (+ bias), M <= 16.
 // The weights are streamed once from HBM at full width; that is all this kernel is about.
 //
-//   A block owns 16 rows of W (for the SwiGLU form: 16 gate rows and the 16 up rows that go with
-//   them). Its 8 warps take the 32-wide K blocks in turn (warp w: blocks w, w+8, ...), so together
+//   A block owns 16 rows of W (for the SwiGLU form: 8 gate rows and the 8 up rows that go with
+//   them, as the two halves of one tensor-core tile). Its 8 warps take the 32-wide K blocks in turn (warp w: blocks w, w+8, ...), so together
 //   they read 512 contiguous bytes of each row per round. A lane loads 16 bytes of two W rows and
 //   16 bytes of one x row per block; the tensor core (m16n8k16, f32 accumulation) sees W as the
 //   A operand and x as B, both with the same permutation of K inside a block, which a dot product
@@ -34,19 +34,20 @@ template <int NT, int GLU, int U, typename TO>
 __global__ void __launch_bounds__(GS_WARPS * 32) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
                                                                     const __nv_bfloat16* __restrict__ W, int ldw, TO* __restrict__ out,
                                                                     int ldo, const float* __restrict__ bias, float alpha, int M, int N, int K) {
-    constexpr int NW = GLU ? 2 : 1;               // weight row sets: gate and up
+    constexpr int NW = 1;
+    constexpr int ROWS = GLU ? 8 : 16;            // outputs per activation row and tile: 16 rows, or 8 gate rows with their 8 up rows
     __shared__ float part[GS_WARPS][NW][NT][16][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, c = lane & 3;
-    const int n0 = blockIdx.x * 16;
+    const int n0 = blockIdx.x * ROWS;
     const __nv_bfloat16* wrow[NW][2];
 #pragma unroll
     for (int s = 0; s < NW; ++s)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            int n = n0 + r + 8 * h;
+            int n = GLU ? n0 + r : n0 + r + 8 * h;
             if (n > N - 1) n = N - 1;             // rows past the end are computed and dropped
-            wrow[s][h] = W + ((size_t)s * N + n) * ldw;
+            wrow[s][h] = W + ((size_t)(GLU ? h : 0) * N + n) * ldw;
         }
     const __nv_bfloat16* xrow[NT];
 #pragma unroll
@@ -96,21 +97,22 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_skinny_kernel(const __nv_b
             part[warp][s][t][r + 8][c * 2 + 1] = acc[s][t][3];
         }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < NT * 8 * 16; idx += GS_WARPS * 32) {
-        const int nl = idx & 15, m = idx >> 4;    // consecutive threads: consecutive output columns
+    for (int idx = threadIdx.x; idx < NT * 8 * ROWS; idx += GS_WARPS * 32) {
+        const int nl = idx % ROWS, m = idx / ROWS;   // consecutive threads: consecutive output columns
         const int n = n0 + nl;
         if (m >= M || n >= N) continue;
         const int t = m >> 3, mc = m & 7;
-        float v[NW];
+        float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int s = 0; s < NW; ++s) {
-            float sum = 0.f;
-#pragma unroll
-            for (int w = 0; w < GS_WARPS; ++w) sum += part[w][s][t][nl][mc];
-            v[s] = alpha * sum + (bias ? bias[(size_t)s * N + n] : 0.f);
+        for (int w = 0; w < GS_WARPS; ++w) {
+            s0 += part[w][0][t][nl][mc];
+            if (GLU) s1 += part[w][0][t][nl + 8][mc];
         }
-        float y = v[0];
-        if (GLU) y = v[0] / (1.f + expf(-v[0])) * v[NW - 1];
+        float y = alpha * s0 + (bias ? bias[n] : 0.f);
+        if (GLU) {
+            const float u = alpha * s1 + (bias ? bias[N + n] : 0.f);
+            y = y / (1.f + expf(-y)) * u;
+        }
         gs_store<TO>(out + (size_t)m * ldo + n, y);
     }
 }
@@ -118,8 +120,9 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_skinny_kernel(const __nv_b
 template <int NT, int GLU, typename TO>
 static void gs_launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, const float* bias, float alpha, int M, int N,
                       int K, cudaStream_t stream) {
-    constexpr int U = (NT == 1 && !GLU) ? 8 : 4;
-    gemm_skinny_kernel<NT, GLU, U, TO><<<(N + 15) / 16, GS_WARPS * 32, 0, stream>>>(
+    constexpr int U = NT == 1 ? 8 : 4;
+    constexpr int ROWS = GLU ? 8 : 16;
+    gemm_skinny_kernel<NT, GLU, U, TO><<<(N + ROWS - 1) / ROWS, GS_WARPS * 32, 0, stream>>>(
         (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, (TO*)out, ldo, bias, alpha, M, N, K);
 }
 
