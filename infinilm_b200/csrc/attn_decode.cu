@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
     float* __restrict__ ml_part) {
     extern __shared__ __align__(16) unsigned char smem[];
+    il_pdl_launch_dependents();
+    il_pdl_wait();
     const int split = blockIdx.x;
     const int G = nh / nkv;
     const int row_tiles = (G + 15) / 16;
@@ -165,6 +167,8 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
                                                                 const int* __restrict__ entry_kvlen, int nh, int n_rows, int window,
                                                                 int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out) {
     __shared__ float fs[4][AD_MAX_SPLITS];
+    il_pdl_launch_dependents();
+    il_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp;        // = e * nh + head
     if (row >= n_rows) return;
@@ -218,12 +222,11 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     }
     const int G = nh / nkv, row_tiles = (G + 15) / 16;
     dim3 grid(n_splits, nkv * row_tiles, n_decode);
-    attn_decode_kernel<<<grid, AD_WARPS * 32, AD_SMEM, stream>>>(
+    IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, AD_SMEM, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
         scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part);
-    IL_LAUNCH_CHECK();
     const int n_rows = n_decode * nh;
-    attn_decode_merge_kernel<<<(n_rows + 3) / 4, 128, 0, stream>>>(o_part, ml_part, entry_kvlen, nh, n_rows, window, pages_per_split,
+    IL_LAUNCH(attn_decode_merge_kernel, (n_rows + 3) / 4, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window, pages_per_split,
                                                                   n_splits, (__nv_bfloat16*)out);
     IL_LAUNCH_CHECK();
     return IL_OK;

@@ -6,6 +6,8 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float scale,
                              float* __restrict__ out, int H, int V, int round_bf16) {
+    il_pdl_launch_dependents();
+    il_pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -27,9 +29,9 @@ IL_EXPORT int il_embed(const int* ids, const void* table, int table_kind, float 
     if (H <= 0 || V <= 0) return IL_BAD_ARG;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_kind == IL_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, scale, out, H, V, round_bf16);
+        IL_LAUNCH(embed_kernel<float>, T, threads, 0, stream, ids, (const float*)table, scale, out, H, V, round_bf16);
     else if (table_kind == IL_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, scale, out, H, V, round_bf16);
+        IL_LAUNCH(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, ids, (const __nv_bfloat16*)table, scale, out, H, V, round_bf16);
     else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();

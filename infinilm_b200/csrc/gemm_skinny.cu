@@ -49,6 +49,8 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_skinny_kernel(const __nv_b
             if (n > N - 1) n = N - 1;             // rows past the end are computed and dropped
             wrow[s][h] = W + ((size_t)(GLU ? h : 0) * N + n) * ldw;
         }
+    il_pdl_launch_dependents();
+    il_pdl_wait();
     const __nv_bfloat16* xrow[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) xrow[t] = (t * 8 + r < M) ? x + (size_t)(t * 8 + r) * ldx : nullptr;
@@ -118,12 +120,12 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_skinny_kernel(const __nv_b
 }
 
 template <int NT, int GLU, typename TO>
-static void gs_launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, const float* bias, float alpha, int M, int N,
+static cudaError_t gs_launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, const float* bias, float alpha, int M, int N,
                       int K, cudaStream_t stream) {
     constexpr int U = NT == 1 ? 8 : 4;
     constexpr int ROWS = GLU ? 8 : 16;
-    gemm_skinny_kernel<NT, GLU, U, TO><<<(N + ROWS - 1) / ROWS, GS_WARPS * 32, 0, stream>>>(
-        (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, (TO*)out, ldo, bias, alpha, M, N, K);
+    return il_launch(gemm_skinny_kernel<NT, GLU, U, TO>, dim3((N + ROWS - 1) / ROWS), dim3(GS_WARPS * 32), 0, stream,
+              (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, (TO*)out, ldo, bias, alpha, M, N, K);
 }
 
 // glu = 1: W is [2N, K] (N gate rows, then N up rows), bias [2N], out[M,N] = silu(alpha*x.Wg^T + bg) * (alpha*x.Wu^T + bu).
@@ -133,15 +135,17 @@ IL_EXPORT int il_gemm_skinny(const void* x, int ldx, const void* W, int ldw, voi
     if (M > 16 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K || ldo < N) return IL_UNSUPPORTED;
     if (out_kind != IL_F32 && out_kind != IL_BF16) return IL_BAD_ARG;
     if (glu && out_kind != IL_BF16) return IL_UNSUPPORTED;
+    cudaError_t e;
     if (M <= 8) {
-        if (glu) gs_launch<1, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
-        else if (out_kind == IL_BF16) gs_launch<1, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
-        else gs_launch<1, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
+        if (glu) e = gs_launch<1, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
+        else if (out_kind == IL_BF16) e = gs_launch<1, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
+        else e = gs_launch<1, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
     } else {
-        if (glu) gs_launch<2, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
-        else if (out_kind == IL_BF16) gs_launch<2, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
-        else gs_launch<2, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
+        if (glu) e = gs_launch<2, 1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
+        else if (out_kind == IL_BF16) e = gs_launch<2, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
+        else e = gs_launch<2, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
     }
+    if (e != cudaSuccess) return 1000 + (int)e;
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

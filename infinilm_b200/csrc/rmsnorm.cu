@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict_
                                                               const void* __restrict__ w, int w_kind, float eps, TA* __restrict__ out,
                                                               const int* __restrict__ rows, int H) {
     __shared__ float red[32];
+    il_pdl_launch_dependents();
+    il_pdl_wait();
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
     float* rr = resid + (size_t)r * H;
@@ -107,11 +109,11 @@ static int launch_vec(float* resid, const void* branch, float bscale, const void
                       const int* rows, int n_rows, int H, cudaStream_t stream) {
     const int nv = H >> 2;
     if (nv <= 256 * 2)
-        add_rmsnorm_vec_kernel<TA, 2><<<n_rows, 256, 0, stream>>>(resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 2>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
     else if (nv <= 256 * 4)
-        add_rmsnorm_vec_kernel<TA, 4><<<n_rows, 256, 0, stream>>>(resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 4>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
     else
-        add_rmsnorm_vec_kernel<TA, 8><<<n_rows, 256, 0, stream>>>(resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
+        IL_LAUNCH((add_rmsnorm_vec_kernel<TA, 8>), n_rows, 256, 0, stream, resid, (const TA*)branch, bscale, w, w_kind, eps, (TA*)out, rows, H);
     return 0;
 }
 

@@ -17,6 +17,8 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const in
                                   const int* __restrict__ tok_entry, const int* __restrict__ block_table,
                                   int bt_stride, TA* __restrict__ cache, int page_size, int nh, int nkv, int hd,
                                   int rot, const float* __restrict__ inv_freq, float mscale) {
+    il_pdl_launch_dependents();
+    il_pdl_wait();
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     TA* row = qkv + (size_t)t * row_stride;
@@ -82,10 +84,10 @@ IL_EXPORT int il_rope_store(void* qkv, int act_kind, int row_stride, const int* 
     if (row_stride < (nh + 2 * nkv) * hd || hd % 16 != 0 || row_stride % 8 != 0) return IL_BAD_ARG;
     const int threads = 256;
     if (act_kind == IL_F32)
-        rope_store_kernel<float><<<T, threads, 0, stream>>>((float*)qkv, row_stride, tok_pos, tok_entry, block_table, bt_stride,
+        IL_LAUNCH(rope_store_kernel<float>, T, threads, 0, stream, (float*)qkv, row_stride, tok_pos, tok_entry, block_table, bt_stride,
                                                             (float*)cache, page_size, nh, nkv, hd, rot, inv_freq, mscale);
     else if (act_kind == IL_BF16)
-        rope_store_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((__nv_bfloat16*)qkv, row_stride, tok_pos, tok_entry, block_table,
+        IL_LAUNCH(rope_store_kernel<__nv_bfloat16>, T, threads, 0, stream, (__nv_bfloat16*)qkv, row_stride, tok_pos, tok_entry, block_table,
                                                                     bt_stride, (__nv_bfloat16*)cache, page_size, nh, nkv, hd, rot,
                                                                     inv_freq, mscale);
     else

@@ -37,6 +37,8 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
     __shared__ int shi[32];
     __shared__ float s_prefix[SP_THREADS];
     __shared__ int s_result;
+    il_pdl_launch_dependents();
+    il_pdl_wait();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * ld;
 
@@ -148,7 +150,7 @@ IL_EXPORT int il_sample(const float* logits, int ld, int R, int V, const float* 
                         const float* top_p, const float* uniform, int* out, cudaStream_t stream) {
     if (R <= 0) return IL_OK;
     if (V <= 0 || ld < V) return IL_BAD_ARG;
-    sample_kernel<<<R, SP_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, uniform, out);
+    IL_LAUNCH(sample_kernel, R, SP_THREADS, 0, stream, logits, ld, V, temperature, top_k, top_p, uniform, out);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
