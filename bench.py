@@ -111,6 +111,48 @@ def weight_bytes(cfg, n_layers):
     return 2 * (per_layer * n_layers + V * H + H), per_layer
 
 
+def profile_step(args) -> int:
+    """One decode step (batch --batch, 2,048 tokens cached) or one 2,048-token prefill step of the benchmark
+    model with --layers layers, bracketed by cudaProfilerStart/Stop; nothing is timed or printed but 'profiled'."""
+    import torch
+
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.engine import Engine, StepEntry
+    from infinilm_b200.weights import random_tensors
+    raw = dict(CONFIG_8B)
+    raw["num_hidden_layers"] = args.layers or 2
+    cfg = config_from_json(raw)
+    B = args.batch
+    eng = Engine.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", page_size=PAGE,
+                              num_pages=B * (PROMPT_LEN // PAGE + 4) + 8, max_seqs=max(B, 2), max_batch_tokens=4096)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in range(B)]
+    if args.profile_step == "decode":
+        seqs = [eng.open(i) for i in range(B)]
+        for s, p in zip(seqs, prompts):
+            eng.step([StepEntry(s, p, [])])
+        for _ in range(2):
+            eng.step([StepEntry(s, [5], [0]) for s in seqs])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        eng.step([StepEntry(s, [5], [0]) for s in seqs])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    else:
+        for i in range(2):
+            s = eng.open(("w", i))
+            eng.step([StepEntry(s, prompts[0], [PROMPT_LEN - 1])])
+            eng.close(s)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        s = eng.open("p")
+        eng.step([StepEntry(s, prompts[0], [PROMPT_LEN - 1])])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    print("profiled")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -121,6 +163,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
+    ap.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
+                    help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off); "
+                         "use with --layers 2 to keep the capture small")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -142,6 +187,8 @@ def main() -> int:
     from infinilm_b200.llm import LLM, SamplingParams
     from infinilm_b200.weights import random_tensors
 
+    if args.profile_step:
+        return profile_step(args)
     raw = dict(CONFIG_8B)
     full_layers = raw["num_hidden_layers"]
     n_layers = args.layers or full_layers
