@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int kvlen = entry_kvlen[e];
     const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
     const int first_page = lo / AD_PAGE, last_page = (kvlen - 1) / AD_PAGE;
+    // pages_per_split 0: this request's pages are divided evenly over the splits
+    if (pages_per_split <= 0) pages_per_split = (last_page - first_page + n_splits) / n_splits;
     const int p0 = first_page + split * pages_per_split;
     int p1 = p0 + pages_per_split;
     if (p1 > last_page + 1) p1 = last_page + 1;
@@ -62,9 +64,17 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
 
     const uint32_t pipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_STAGE_BYTES;
     const int n_my = (p1 - p0 - warp + AD_WARPS - 1) / AD_WARPS;   // pages p0+warp, +4, ...
+    // Page ids of this warp's iterations, 32 at a time: lane l holds the id of iteration base + l, so the
+    // table lookup is off the path that issues the copies.
+    int ids_base = 0;
+    int my_ids = (lane < n_my) ? bt[p0 + warp + lane * AD_WARPS] : 0;
     auto issue = [&](int it) {
         if (it < n_my) {
-            const int page = bt[p0 + warp + it * AD_WARPS];
+            if (it >= ids_base + 32) {
+                ids_base += 32;
+                my_ids = (ids_base + lane < n_my) ? bt[p0 + warp + (ids_base + lane) * AD_WARPS] : 0;
+            }
+            const int page = __shfl_sync(0xffffffffu, my_ids, it - ids_base);
             const uint32_t st = pipe + (it % AD_STAGES) * AD_STAGE_BYTES;
             at_load_page(st, st + AD_PAGE * AT_ROW_BYTES, cache + (size_t)page * page_elems, g, nkv, AD_PAGE, 0, AD_PAGE, lane);
         }
@@ -176,6 +186,7 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
     const int kvlen = entry_kvlen[e];
     const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
     const int n_pages = (kvlen - 1) / AD_PAGE - lo / AD_PAGE + 1;
+    if (pages_per_split <= 0) pages_per_split = (n_pages + n_splits - 1) / n_splits;
     int n_valid = (n_pages + pages_per_split - 1) / pages_per_split;
     if (n_valid > n_splits) n_valid = n_splits;
     const size_t pr0 = (size_t)row * n_splits;
@@ -239,7 +250,7 @@ IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const v
                              cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
-    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split <= 0 || n_splits <= 0) return IL_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
     return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
                      pages_per_split, n_splits, o_part, ml_part, stream);

@@ -16,7 +16,7 @@ int il_attn_decode_noalloc(const void* qkv, int row_stride, void* out, const voi
                            float scale, int window, int pages_per_split, int n_splits, cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
-    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split <= 0 || n_splits <= 0) return IL_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     const long long rows = (long long)n_decode * nh * n_splits;
     if (rows > IL_NOALLOC_MAX_ROWS) return IL_NOALLOC_TOO_LARGE;
     if (n_splits > AD_MAX_SPLITS) return IL_NOALLOC_TOO_LARGE;

@@ -246,6 +246,7 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
                      head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
                      o_part: torch.Tensor, ml_part: torch.Tensor) -> None:
     """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each).
+    pages_per_split 0: each request's pages are divided evenly over the n_splits splits.
     Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
     _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:

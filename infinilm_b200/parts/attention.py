@@ -81,7 +81,7 @@ class Attention(Mixer):
     # else, and the whole float32 path, runs the plain kernel.
     FAST_PAGE = 16
     FAST_MAX_GROUP = 64
-    TARGET_BLOCKS = 2 * 148                       # decode splits aim at about two blocks per SM
+    TARGET_BLOCKS = 2 * 148                       # blocks of the decode kernel that are resident at once (two per SM)
 
     def attend(self, qkv, out, ctx, cache) -> None:
         G = self.nh // self.nkv
@@ -97,12 +97,11 @@ class Attention(Mixer):
                 max_len = min(max_len, self.window + self.FAST_PAGE)
             max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.window is not None else 0)
             base = n_dec * self.nkv * ((G + 15) // 16)
-            n_splits = max(1, min((self.TARGET_BLOCKS + base - 1) // base, (max_pages + 3) // 4, 128))
-            pps = (max_pages + n_splits - 1) // n_splits
-            n_splits = (max_pages + pps - 1) // pps
+            # as many splits as fill one wave of blocks (two per SM), never more: a second, part-filled wave costs more
+            n_splits = max(1, min(self.TARGET_BLOCKS // base, (max_pages + 3) // 4, 128))
             rows = n_dec * self.nh * n_splits
             ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
-                                 self.nh, self.nkv, self.hd, self.scale, self.window, pps, n_splits,
+                                 self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
                                  ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
                                  ctx.ws.flat("attn_ml_part", rows * 2, torch.float32))
         if E > n_dec:

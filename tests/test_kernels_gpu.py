@@ -239,6 +239,13 @@ def test_attention_decode_bf16(cuda_device, nh, nkv, hd, window, splits):
     ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
                          window, pps, n_splits, o_part, ml_part)
     close(out.cpu(), c["ref"], "bfloat16")
+    # pages_per_split 0: every request divides its own pages evenly over the splits
+    out.fill_(float("nan"))
+    o_part = torch.full((E * nh * splits * hd,), float("nan"), device="cuda")
+    ml_part = torch.full((E * nh * splits * 2,), float("nan"), device="cuda")
+    ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
+                         window, 0, splits, o_part, ml_part)
+    close(out.cpu(), c["ref"], "bfloat16")
 
 
 # -- sampling --------------------------------------------------------------------------------------
