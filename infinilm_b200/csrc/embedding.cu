@@ -37,3 +37,20 @@ IL_EXPORT int il_embed(const int* ids, const void* table, int table_kind, float 
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
+
+// token_ids[rows[i]] = src[src_idx[i]]: puts tokens that were sampled on the device (and not read by the host yet)
+// into the next step's token list. Out-of-vocabulary values are caught by the gather above.
+__global__ void patch_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ rows, const int* __restrict__ src_idx,
+                                    const int* __restrict__ src, int n) {
+    il_pdl_launch_dependents();
+    il_pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) token_ids[rows[i]] = src[src_idx[i]];
+}
+
+IL_EXPORT int il_patch_tokens(int* token_ids, const int* rows, const int* src_idx, const int* src, int n, cudaStream_t stream) {
+    if (n <= 0) return IL_OK;
+    IL_LAUNCH(patch_tokens_kernel, (n + 127) / 128, 128, 0, stream, token_ids, rows, src_idx, src, n);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}

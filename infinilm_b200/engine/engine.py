@@ -82,8 +82,8 @@ class Engine:
     def close(self, seq: SequenceCache) -> None:
         self.cache.close(seq)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        return self.runner.step(entries)
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.runner.step(entries, device_tokens)
 
     def enable_graphs(self) -> None:
         """Replay decode-only steps as CUDA graphs from now on."""

@@ -63,6 +63,8 @@ class Request:
     arrival: int = 0
     n_preempted: int = 0
     sample_stream: int = 0                        # which stream of uniform numbers this request draws from
+    last_sample_row: int = -1                     # row of this request in the sampler output of the step that last sampled for it
+    closing: bool = False                         # its last token is on its way (max_tokens reached): schedule it no more
 
     @property
     def all_token_ids(self) -> List[int]:
@@ -77,11 +79,15 @@ class Request:
         return self.status in (RequestStatus.FINISHED, RequestStatus.ABORTED)
 
 
+PENDING = -1     # placeholder in output_token_ids for a token that was sampled on the device and not read back yet
+
+
 @dataclass
 class ScheduledEntry:
     request: Request
-    tokens: List[int]
+    tokens: List[int]                             # PENDING stands for the token the previous step sampled for this request
     samples: bool                                 # the logits of the last token are wanted (and sampled from)
+    out_index: int = -1                           # where in output_token_ids the sampled token goes
 
 
 @dataclass
@@ -207,8 +213,8 @@ class Scheduler:
             return need if need <= free else -1
 
         # 1. running requests, decoding ones first (one token each), then unfinished prompts, oldest first
-        decoding = [r for r in self.running if len(r.all_token_ids) - r.n_cached == 1]
-        filling = [r for r in self.running if len(r.all_token_ids) - r.n_cached > 1]
+        decoding = [r for r in self.running if not r.closing and len(r.all_token_ids) - r.n_cached == 1]
+        filling = [r for r in self.running if not r.closing and len(r.all_token_ids) - r.n_cached > 1]
         for r in sorted(decoding, key=lambda r: r.arrival) + sorted(filling, key=lambda r: r.arrival):
             if r not in self.running:             # preempted a moment ago
                 continue
@@ -263,30 +269,60 @@ class Scheduler:
             self.cache.close(r.seq)
             r.seq = None
 
-    def update(self, out: SchedulerOutput, sampled: Dict[str, int]) -> List[Request]:
-        """`sampled[request_id]` is the token drawn for each entry that sampled. Appends it,
-        applies the finish rules, frees what finished requests held. Returns them."""
-        finished = []
+    def launched(self, out: SchedulerOutput) -> None:
+        """The step has been issued: every entry that samples gets a PENDING place in its request's
+        output (the token is on the device); a request whose output is now max_tokens long is not
+        scheduled again (`closing`), so no step runs past a length limit."""
+        row = 0
         for e in out.entries:
-            r = e.request
-            if not e.samples or r.finished:
+            if not e.samples:
                 continue
-            tok = int(sampled[r.request_id])
-            r.output_token_ids.append(tok)
+            r = e.request
+            e.out_index = len(r.output_token_ids)
+            r.output_token_ids.append(PENDING)
+            r.last_sample_row = row
+            row += 1
+            if len(r.output_token_ids) >= r.params.max_tokens or (
+                    self.max_model_len is not None and len(r.all_token_ids) >= self.max_model_len):
+                r.closing = True
+
+    def retire(self, out: SchedulerOutput, sampled: Sequence[int]) -> List[Request]:
+        """The tokens of a step have been read back (`sampled[i]` for its i-th sampling entry): they
+        take their places, the finish rules apply, finished requests give back what they hold. A
+        request that ended on an earlier token (end of sequence) while this step already ran ahead
+        for it simply drops the token. Returns the requests that finished."""
+        finished = []
+        row = -1
+        for e in out.entries:
+            if not e.samples:
+                continue
+            row += 1
+            r = e.request
+            if r.finished:
+                continue
+            tok = int(sampled[row])
+            r.output_token_ids[e.out_index] = tok
             p = r.params
             if not p.ignore_eos and tok in r.eos_token_ids:
                 reason = FinishReason.EOS_TOKEN
             elif tok in p.stop_token_ids:
                 reason = FinishReason.STOP
-            elif len(r.output_token_ids) >= p.max_tokens:
+            elif e.out_index + 1 >= p.max_tokens:
                 reason = FinishReason.LENGTH
-            elif self.max_model_len is not None and len(r.all_token_ids) >= self.max_model_len:
+            elif self.max_model_len is not None and len(r.prompt_token_ids) + e.out_index + 1 >= self.max_model_len:
                 reason = FinishReason.LENGTH
             else:
                 continue
+            del r.output_token_ids[e.out_index + 1:]      # a token a later step ran ahead for is dropped
             self._finish(r, reason)
             finished.append(r)
         return finished
+
+    def update(self, out: SchedulerOutput, sampled: Dict[str, int]) -> List[Request]:
+        """Launch and retire in one call, for a caller that reads every step's tokens before the next
+        step: `sampled[request_id]` is the token drawn for each entry that sampled."""
+        self.launched(out)
+        return self.retire(out, [sampled[e.request.request_id] for e in out.entries if e.samples])
 
     def stats(self) -> Dict[str, int]:
         return {"waiting": len(self.waiting), "running": len(self.running), "free_pages": self._free_pages(),

@@ -129,9 +129,12 @@ class StepRunner:
         return self._desc_ring[self._desc_i], self._desc_dev
 
     # -- the step ----------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the order of
-        `entries` and of each entry's `want`."""
+        `entries` and of each entry's `want`.
+
+        A token given as -(1 + i) is not known to the host yet: it is taken from `device_tokens[i]`
+        (int32 on the device, e.g. what the sampler drew in the step before) when the step runs."""
         if not entries:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.device)
         vocab = self.model.vocab
@@ -148,7 +151,7 @@ class StepRunner:
             for w in e.want:
                 if not 0 <= w < n:
                     raise StepError(f"entry {i} ({e.seq.seq_id!r}): wanted place {w} is outside its {n} tokens")
-            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+            if max(e.tokens) >= vocab or (min(e.tokens) < 0 and device_tokens is None):
                 raise StepError(f"request {e.seq.seq_id!r}: token id outside [0, {vocab})")
             if max_pos is not None and e.seq.length + n > max_pos:
                 raise StepError(f"request {e.seq.seq_id!r} would pass max_position_embeddings {max_pos}")
@@ -196,7 +199,16 @@ class StepRunner:
             want_rows = list(range(Ep))           # row k of the logits belongs to sorted entry k
         n_want = len(want_rows)
 
-        n_ints = 3 * Tp + (Ep + 1) + Ep + max(n_want, 1) + 2 * Ep + sum(Ep * w for w in widths.values())
+        patches = []                              # (token row, index into device_tokens)
+        if device_tokens is not None:
+            for i, e in enumerate(entries):
+                for j, t in enumerate(e.tokens):
+                    if t < 0:
+                        if -1 - t >= device_tokens.numel():
+                            raise StepError(f"request {e.seq.seq_id!r}: device token {-1 - t} does not exist")
+                        patches.append((qstart[row_of_entry[i]] + j, -1 - t))
+        n_patch = Tp if graph_key is not None else len(patches)       # a replayed step's buffer is sized once, for any number
+        n_ints = (3 * Tp + (Ep + 1) + Ep + max(n_want, 1) + 2 * Ep + sum(Ep * w for w in widths.values()) + 2 * n_patch)
         host, dev = self._desc(n_ints)
         if graph_key is not None:
             gs = self._graphs.get(graph_key)
@@ -214,12 +226,13 @@ class StepRunner:
         s_tok, s_pos, s_ent = take(Tp), take(Tp), take(Tp)
         s_qs, s_kv, s_want, s_rs, s_wsl = take(Ep + 1), take(Ep), take(max(n_want, 1)), take(Ep), take(Ep)
         s_bt = {g: take(Ep * widths[g]) for g in paged}
+        s_prow, s_psrc = take(n_patch), take(n_patch)
         h_qlen, h_kvlen = [], []
         for k, i in enumerate(order):
             e = entries[i]
             n, start = len(e.tokens), e.seq.length
             a, b = qstart[k], qstart[k + 1]
-            h[s_tok[0] + a: s_tok[0] + b] = np.asarray(e.tokens, dtype=np.int64)
+            h[s_tok[0] + a: s_tok[0] + b] = np.maximum(np.asarray(e.tokens, dtype=np.int64), 0)
             h[s_pos[0] + a: s_pos[0] + b] = np.arange(start, start + n, dtype=np.int32)
             h[s_ent[0] + a: s_ent[0] + b] = k
             h[s_kv[0] + k] = start + n
@@ -251,7 +264,13 @@ class StepRunner:
         h[s_qs[0]: s_qs[1]] = qstart
         if n_want:
             h[s_want[0]: s_want[0] + n_want] = want_rows
+        if patches:
+            h[s_prow[0]: s_prow[0] + len(patches)] = [p[0] for p in patches]
+            h[s_psrc[0]: s_psrc[0] + len(patches)] = [p[1] for p in patches]
         dev[:off].copy_(host[:off], non_blocking=True)
+        if patches:                               # tokens the host has not seen: copied in on the device
+            ops.patch_tokens(dev[s_tok[0]: s_tok[1]], dev[s_prow[0]: s_prow[0] + len(patches)],
+                             dev[s_psrc[0]: s_psrc[0] + len(patches)], device_tokens)
         ev = torch.cuda.Event()
         ev.record()
         self._desc_events[self._desc_i] = ev

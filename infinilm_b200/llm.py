@@ -52,10 +52,11 @@ class LLM:
                  temperature: float = 1.0, top_p: float = 0.8, top_k: int = 1, enable_graph: bool = False,
                  attn_backend: str = "default", skip_load: bool = False, enable_prefix_caching: bool = False,
                  max_num_batched_tokens: Optional[int] = None, chunk_size: int = 2048, seed: int = 0,
-                 admission: str = "worst_case", _config: Optional[ModelConfig] = None,
+                 admission: str = "worst_case", pipelined: bool = True, _config: Optional[ModelConfig] = None,
                  _tensors: Optional[Mapping[str, torch.Tensor]] = None):
         """`model_path`: folder with config.json and safetensors. `skip_load`: random weights
-        (seeded) instead of the folder's. `num_blocks` pages of `block_size` tokens."""
+        (seeded) instead of the folder's. `num_blocks` pages of `block_size` tokens. `pipelined`: a
+        step's tokens are read back while the next step runs (the next step gets them on the device)."""
         if tensor_parallel_size != 1 or pipeline_parallel_size != 1:
             raise ValueError("this engine runs on one GPU: tensor_parallel_size and pipeline_parallel_size must be 1")
         if cache_type != "paged":
@@ -92,7 +93,12 @@ class LLM:
         self.model_path = model_path
         self._tokenizer = None
         self._n_requests = 0
-        self._ids_host = torch.empty(max(max_batch_size, 8), dtype=torch.int32, pin_memory=True)
+        nrow = max(max_batch_size, 8)
+        self._ids_host = [torch.empty(nrow, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._ids_dev = [torch.zeros(nrow, dtype=torch.int32, device=self.engine.device) for _ in range(2)]
+        self._parity = 0
+        self._inflight = None                     # the step whose tokens the host has not read yet
+        self.pipelined = pipelined
         if enable_graph:
             self.engine.enable_graphs()
 
@@ -134,26 +140,52 @@ class LLM:
         return r
 
     def step(self) -> List[Request]:
-        """One step: schedule, run, sample, update. Returns the requests that finished."""
+        """One step: schedule, run, sample; then read back the tokens of the step BEFORE this one and
+        apply the finish rules to them. The step just issued stays in flight: its tokens are fed to
+        the next step on the device, so the host never waits for the GPU between two steps. Returns
+        the requests that finished. When nothing is left to schedule, the step in flight is retired."""
         out = self.scheduler.schedule()
         if not out.entries:
+            if self._inflight is not None:
+                return self._retire()
             if self.scheduler.has_work():
                 raise RuntimeError("the scheduler has requests but could schedule none (pool too small?)")
             return []
-        entries = [StepEntry(e.request.seq, e.tokens, [len(e.tokens) - 1] if e.samples else []) for e in out.entries]
-        logits = self.engine.step(entries)
+        entries = []
+        for e in out.entries:
+            toks = e.tokens
+            if toks[-1] < 0:                      # sampled by the step in flight: row of that step's sampler output
+                toks = toks[:-1] + [-(1 + e.request.last_sample_row)]
+            entries.append(StepEntry(e.request.seq, toks, [len(toks) - 1] if e.samples else []))
+        prev_ids = self._ids_dev[self._parity ^ 1] if self._inflight is not None else None
+        logits = self.engine.step(entries, prev_ids)
         rows = [e for e in out.entries if e.samples]
-        sampled: Dict[str, int] = {}
+        ids_dev = self._ids_dev[self._parity]
+        host = self._ids_host[self._parity]
+        ev = None
         if rows:
             params = [e.request.params for e in rows]
             us = [uniform01(e.request.params.seed if e.request.params.seed is not None else self.seed,
                             e.request.sample_stream, len(e.request.output_token_ids)) for e in rows]
-            ids = self.sampler.sample(logits, params, us)
-            host = self._ids_host[:len(rows)]
-            host.copy_(ids, non_blocking=False)
-            for e, t in zip(rows, host.tolist()):
-                sampled[e.request.request_id] = t
-        return self.scheduler.update(out, sampled)
+            self.sampler.sample(logits, params, us, out=ids_dev)
+            host[:len(rows)].copy_(ids_dev[:len(rows)], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        self.scheduler.launched(out)
+        finished = self._retire() if self._inflight is not None else []
+        self._inflight = (out, len(rows), host, ev)
+        self._parity ^= 1
+        if not self.pipelined:
+            finished += self._retire()
+        return finished
+
+    def _retire(self) -> List[Request]:
+        """Waits for the tokens of the step in flight and hands them to the scheduler."""
+        out, n, host, ev = self._inflight
+        self._inflight = None
+        if ev is not None:
+            ev.synchronize()
+        return self.scheduler.retire(out, host[:n].tolist())
 
     # -- batch generation --------------------------------------------------------------------
     def generate(self, prompts: Union[str, List[str], None] = None, messages=None,
@@ -209,4 +241,6 @@ class LLM:
         return s
 
     def close(self) -> None:
+        if self._inflight is not None:
+            self._retire()
         self.engine.synchronize()

@@ -107,6 +107,16 @@ def embed(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tenso
              _stream()), "embed")
 
 
+def patch_tokens(token_ids: torch.Tensor, rows: torch.Tensor, src_idx: torch.Tensor, src: torch.Tensor) -> None:
+    """token_ids[rows[i]] = src[src_idx[i]], all int32 on the device."""
+    _need_cuda(token_ids, rows, src_idx, src)
+    for t in (token_ids, rows, src_idx, src):
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise KernelError("patch_tokens: contiguous int32 tensors")
+    f = _fn("embedding", "il_patch_tokens", [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p])
+    _check(f(_ptr(token_ids), _ptr(rows), _ptr(src_idx), _ptr(src), rows.numel(), _stream()), "patch_tokens")
+
+
 def add_rmsnorm(resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scale: float, weight: torch.Tensor,
                 eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
     """resid += branch_scale * branch (f32, in place); out = RMSNorm(resid) * weight.

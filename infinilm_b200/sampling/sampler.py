@@ -79,15 +79,18 @@ class Sampler:
         self._dev = torch.empty((4, max_rows), dtype=torch.float32, device=self.device)
         self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
 
-    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], uniforms: Sequence[float]) -> torch.Tensor:
-        """logits float32 [R,V] on the device -> int32 [R] on the device."""
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], uniforms: Sequence[float],
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """logits float32 [R,V] on the device -> int32 [R] on the device (into `out` if given)."""
         R, V = logits.shape
+        if out is None:
+            out = self._out
         if R == 0:
-            return self._out[:0]
+            return out[:0]
         if R > self.max_rows or len(params) != R or len(uniforms) != R:
             raise ValueError("sampler: rows, params and uniforms must agree (and fit max_rows)")
         if all(p.greedy for p in params):
-            return self.argmax(logits)
+            return self.argmax(logits, out)
         hn = self._host_np
         hn[0, :R] = [0.0 if p.greedy else p.temperature for p in params]
         self._host_np_i[1, :R] = [1 if p.greedy else int(p.top_k) for p in params]
@@ -95,12 +98,14 @@ class Sampler:
         hn[3, :R] = list(uniforms)
         self._dev[:, :R].copy_(self._host[:, :R], non_blocking=True)
         ops.sample(logits, self._dev[0, :R], self._dev[1, :R].view(torch.int32), self._dev[2, :R], self._dev[3, :R],
-                   self._out[:R])
-        return self._out[:R]
+                   out[:R])
+        return out[:R]
 
-    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+    def argmax(self, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         R = logits.shape[0]
-        if R > self.max_rows:
+        if out is None:
+            out = self._out
+        if R > self.max_rows or R > out.numel():
             raise ValueError("sampler: too many rows")
-        ops.sample(logits, None, None, None, None, self._out[:R], greedy=True)
-        return self._out[:R]
+        ops.sample(logits, None, None, None, None, out[:R], greedy=True)
+        return out[:R]

@@ -181,3 +181,64 @@ def test_random_traffic_keeps_every_invariant(seed, admission):
     assert cache.free_pages() == {0: 20} and not cache.live
     if admission == "worst_case":
         assert s.n_preemptions == 0
+
+
+def run_pipelined(cache, sched, token_of, max_steps=500):
+    """LLM.step's order of events without a model: the tokens of a step are read one step late."""
+    inflight = None
+    steps = []
+    for _ in range(max_steps):
+        out = sched.schedule()
+        if not out.entries:
+            if inflight is None:
+                break
+            o, toks = inflight
+            sched.retire(o, toks)
+            inflight = None
+            continue
+        for e in out.entries:
+            assert e.tokens.count(-1) <= 1 and (-1 not in e.tokens or e.tokens[-1] == -1)
+            cache.reserve(e.request.seq, e.request.n_cached + len(e.tokens))
+        for e in out.entries:
+            cache.commit(e.request.seq, e.request.n_cached + len(e.tokens))
+        toks = [token_of(e.request) for e in out.entries if e.samples]
+        sched.launched(out)
+        if inflight is not None:
+            sched.retire(*inflight)
+        inflight = (out, toks)
+        steps.append(out)
+        cache.check_invariants()
+    return steps
+
+
+def test_pipelined_steps_run_one_token_ahead_and_drop_it_after_eos():
+    cache, s = make(num_pages=32)
+    a, b = req(0, 5, max_tokens=6), req(1, 7, max_tokens=20)
+    s.add_request(a), s.add_request(b)
+    # b's third token is its end-of-sequence token (0); a runs to its length limit
+    seq_b = iter([5, 5, 0, 5, 5, 5, 5])
+    steps = run_pipelined(cache, s, lambda r: next(seq_b) if r is b else 5)
+    assert a.output_token_ids == [5] * 6 and a.finish_reason is FinishReason.LENGTH
+    assert b.output_token_ids == [5, 5, 0] and b.finish_reason is FinishReason.EOS_TOKEN
+    n_b = sum(1 for o in steps for e in o.entries if e.request is b)
+    assert n_b == 4                               # prompt, two decodes, and one step that ran ahead of the eos check
+    n_a = sum(1 for o in steps for e in o.entries if e.request is a)
+    assert n_a == 6                               # a length limit is known in advance: nothing runs past it
+    assert cache.free_pages() == {0: 32} and not s.has_work()
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_pipelined_random_traffic(seed):
+    rng = random.Random(seed)
+    cache, s = make(num_pages=24, admission="optimistic", max_num_batched_tokens=40, chunk_size=16, max_batch_size=4)
+    reqs = [req(i, rng.randint(1, 60), max_tokens=rng.randint(1, 30)) for i in range(12)]
+    for r in reqs:
+        s.add_request(r)
+    run_pipelined(cache, s, lambda r: rng.choice([0, 5, 5, 5, 5, 5, 5, 5, 5]), max_steps=4000)
+    assert all(r.finished for r in reqs) and all(-1 not in r.output_token_ids for r in reqs)
+    for r in reqs:
+        if r.finish_reason is FinishReason.EOS_TOKEN:
+            assert r.output_token_ids[-1] == 0 and 0 not in r.output_token_ids[:-1]
+        else:
+            assert len(r.output_token_ids) == r.params.max_tokens and 0 not in r.output_token_ids[:-1]
+    assert cache.free_pages() == {0: 24} and not cache.live
