@@ -163,6 +163,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
+    ap.add_argument("--points", type=str, default="1,64", help="batch sizes of the extra decode points")
     ap.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
                     help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off); "
                          "use with --layers 2 to keep the capture small")
@@ -199,7 +200,7 @@ def main() -> int:
     dev = "cuda:0"
     torch.cuda.set_device(0)
     K, W = args.steps, args.warmup
-    max_b = max(args.batch, 1 if args.no_points else 64)
+    max_b = max([args.batch] + ([] if args.no_points else [int(b) for b in args.points.split(',') if b]))
     pages_per_req = (PROMPT_LEN + 2 * (K + W) + 8 + PAGE - 1) // PAGE + 1
     num_pages = max_b * pages_per_req + 8
 
@@ -277,7 +278,7 @@ def main() -> int:
     achieved = bytes_step / (ms_step / 1e3) / 1e9
     points = {}
     if not args.no_points:
-        for B in (1, 64):
+        for B in [int(b) for b in args.points.split(',') if b]:
             ms_b, _, _, _ = time_decode(B)
             points[f"decode_b{B}"] = B / (ms_b / 1e3)
 

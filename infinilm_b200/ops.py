@@ -352,3 +352,40 @@ def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: floa
                                               _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), kind_of(out.dtype), out.stride(0), _ptr(bias), alpha,
              M, N, K, int(glu), _ptr(stream_status(x.device)), _stream()), "gemm_stream")
+
+
+TC5_MAX_ROWS = 256
+
+
+def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0, bias: Optional[torch.Tensor] = None,
+             scratch: Optional[torch.Tensor] = None) -> None:
+    """out[M,N] = alpha * x[M,K] @ w[N,K]^T (+ bias) on the tcgen05 tensor cores (TMA-fed, accumulators in TMEM),
+    M <= 256, bfloat16 inputs, out bfloat16 or float32. `scratch`: float32 buffer of `gemm_tc5_scratch_bytes` bytes
+    (needed when the kernel slices K to fill the SMs)."""
+    _need_cuda(x, w, out, bias, scratch)
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_tc5: bfloat16 x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_tc5: innermost dimension must be contiguous")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_tc5: bias float32 [N]")
+    need = gemm_tc5_scratch_bytes(M, N, K)
+    if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() * 4 < need):
+        raise KernelError(f"gemm_tc5: needs {need} bytes of float32 scratch")
+    f = _fn("gemm_tc5", "il_gemm_tc5", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_float,
+                                        _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), kind_of(out.dtype), out.stride(0), _ptr(bias), alpha,
+             M, N, K, _ptr(scratch), _ptr(stream_status(x.device)), _stream()), "gemm_tc5")
+
+
+def gemm_tc5_scratch_bytes(M: int, N: int, K: int) -> int:
+    lib = build.load("gemm_tc5")
+    fn = lib.il_gemm_tc5_scratch_bytes
+    fn.argtypes, fn.restype = [_c_int, _c_int, _c_int], ctypes.c_longlong
+    return int(fn(M, N, K))
+
+
+def tc5_ok(M: int, K: int) -> bool:
+    return SKINNY_MAX_ROWS < M <= TC5_MAX_ROWS and K % 8 == 0

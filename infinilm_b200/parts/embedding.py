@@ -45,7 +45,7 @@ class OutputHead(Part):
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
         self.vocab, self.hidden = int(params["vocab"]), int(params["hidden"])
-        self.linear = Linear(self.hidden, self.vocab, dtype, alpha=float(params.get("scale", 1.0)))
+        self.linear = Linear(self.hidden, self.vocab, dtype, alpha=float(params.get("scale", 1.0)), use_tc5=True)
         self.tied_to = params.get("tied_to")
 
     def weight_specs(self) -> List[WeightSpec]:

@@ -347,3 +347,23 @@ def test_gemm_stream_equals_skinny(cuda_device, M, N, K, glu):
     ref = (torch.nn.functional.silu(y[:, :N]) * y[:, N:]) if glu else y
     close(c, ref.float(), "bfloat16")
     assert torch.equal(a, c)
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 97, 64), (32, 128, 64), (64, 331, 200), (200, 513, 1000), (64, 4096, 4096), (256, 300, 264),
+                                   (33, 73448, 256)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+def test_gemm_tc5(cuda_device, M, N, K, out_dtype):
+    """The tcgen05/TMA product (accumulators in tensor memory) against a float64 reference; its bounded waits never ran out."""
+    g = torch.Generator(device="cuda").manual_seed(12)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=DT[out_dtype])
+    scratch = torch.empty(max(ops.gemm_tc5_scratch_bytes(M, N, K) // 4, 1), device="cuda")
+    ops.gemm_tc5(x, w, out, 0.7, b, scratch)
+    torch.cuda.synchronize()
+    assert int(ops.stream_status("cuda:0").item()) == 0
+    ref = 0.7 * (x.double() @ w.double().t()) + b.double()
+    close(out, ref.float(), "float32" if out_dtype == "float32" else "bfloat16")
+    ops.gemm_tc5(x, w, out, 1.0, None, scratch)
+    close(out, (x.double() @ w.double().t()).float(), "float32" if out_dtype == "float32" else "bfloat16")
