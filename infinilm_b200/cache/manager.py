@@ -91,6 +91,7 @@ class CacheGroup:
     entries: List[int]                            # run-order indices that own a cache in this group
     pool: Optional[PagePool] = None               # paged_kv groups
     storage: Dict[int, object] = field(default_factory=dict)   # run-order index -> device tensor
+    tma_maps: Dict[int, object] = field(default_factory=dict)  # run-order index -> tensor map of its storage (or absent)
 
 
 @dataclass
@@ -151,6 +152,11 @@ class CacheManager:
                     shape = (self.slots.n_slots,) + tuple(n.shape)
                     dt = torch.float32 if n.dtype == "float32" else self.dtype
                 grp.storage[i] = torch.zeros(shape, dtype=dt, device=self.device)
+                if n.kind == "paged_kv" and dt == torch.bfloat16 and self.page_size == 16:
+                    from .. import ops
+                    m = ops.kv_tensor_map(grp.storage[i])
+                    if m is not None:
+                        grp.tma_maps[i] = m
 
     def bytes_per_token(self, elem_size: int) -> int:
         b = 0
@@ -267,6 +273,7 @@ class PagedKVView:
     page_size: int
     writable: bool = True
     max_pages: int = 0                            # width in use this step
+    tma_map: object = None                        # tensor map of `storage` for kernels that copy pages by TMA
 
 
 @dataclass

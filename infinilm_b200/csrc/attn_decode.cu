@@ -11,22 +11,54 @@
 //
 // Token t (= entry t; decode entries come first in a step) has kv length entry_kvlen[t]; its query
 // sits at position kvlen-1 and sees positions max(0, kvlen-window) .. kvlen-1 (window <= 0: all).
+//
+// Two ways of bringing pages into shared memory. With a tensor map of the layer's cache (head_dim a
+// multiple of 64) one lane per warp issues TMA tensor copies with the 128-byte swizzle, [16 keys x 64]
+// boxes completing on the warp's own mbarriers, and ldmatrix reads the swizzled tiles; small per-lane
+// cp.async copies top out near 3 TB/s on this part, the tensor copies do not. Without a map (other
+// head sizes) the per-lane cp.async path with padded rows is used.
+#include <cuda.h>
+#include <cstring>
+
 #include "attn_mma.cuh"
 
 constexpr int AD_WARPS = 4;
 constexpr int AD_PAGE = 16;                       // keys per tile = page size this kernel takes
-constexpr int AD_STAGES = (HEAD_DIM <= 128) ? 3 : 2;      // 4 warps x 3 stages of a page: two blocks fit on an SM at head_dim 128
+constexpr int AD_STAGES = 2;                      // 4 warps x 2 stages of a page (8-9 KB at head_dim 128): three blocks fit on an SM
 constexpr int AD_STAGE_BYTES = 2 * AD_PAGE * AT_ROW_BYTES;
 constexpr int AD_SMEM_PIPE = AD_WARPS * AD_STAGES * AD_STAGE_BYTES;
 constexpr int AD_SMEM_MERGE = AD_WARPS * 16 * (HEAD_DIM + 2) * 4;
-constexpr int AD_SMEM = AD_SMEM_PIPE > AD_SMEM_MERGE ? AD_SMEM_PIPE : AD_SMEM_MERGE;
+constexpr int AD_SMEM = (AD_SMEM_PIPE > AD_SMEM_MERGE ? AD_SMEM_PIPE : AD_SMEM_MERGE) + AD_WARPS * AD_STAGES * 8 + 1024;
+constexpr bool AD_TMA_OK = (HEAD_DIM % 64 == 0);
+constexpr int AD_BOXES = HEAD_DIM / 64;           // 64-column boxes of a K (or V) block
+constexpr int AD_TMA_STAGE_BYTES = 2 * AD_BOXES * 2048;   // K boxes then V boxes, each [16 x 64] bf16 = 2 KB
+constexpr unsigned AD_SPIN_LIMIT = 1u << 26;
+
+__device__ __forceinline__ bool ad_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (unsigned spin = 0; spin < AD_SPIN_LIMIT; ++spin) {
+        uint32_t done;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void ad_tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// Address of the 16-byte chunk `ch` of row `r` in a block of [16 x head_dim] stored as 64-column boxes with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t ad_swz(uint32_t block, int r, int ch) {
+    return block + (ch >> 3) * 2048 + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+}
 
 __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ qkv, int row_stride, const __nv_bfloat16* __restrict__ cache,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
-    float* __restrict__ ml_part) {
-    extern __shared__ __align__(16) unsigned char smem[];
+    float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, int use_tma, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     il_pdl_launch_dependents();
     il_pdl_wait();
     const int split = blockIdx.x;
@@ -62,35 +94,20 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    const uint32_t pipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_STAGE_BYTES;
     const int n_my = (p1 - p0 - warp + AD_WARPS - 1) / AD_WARPS;   // pages p0+warp, +4, ...
     // Page ids of this warp's iterations, 32 at a time: lane l holds the id of iteration base + l, so the
     // table lookup is off the path that issues the copies.
     int ids_base = 0;
     int my_ids = (lane < n_my) ? bt[p0 + warp + lane * AD_WARPS] : 0;
-    auto issue = [&](int it) {
-        if (it < n_my) {
-            if (it >= ids_base + 32) {
-                ids_base += 32;
-                my_ids = (ids_base + lane < n_my) ? bt[p0 + warp + (ids_base + lane) * AD_WARPS] : 0;
-            }
-            const int page = __shfl_sync(0xffffffffu, my_ids, it - ids_base);
-            const uint32_t st = pipe + (it % AD_STAGES) * AD_STAGE_BYTES;
-            at_load_page(st, st + AD_PAGE * AT_ROW_BYTES, cache + (size_t)page * page_elems, g, nkv, AD_PAGE, 0, AD_PAGE, lane);
+    auto page_of = [&](int it) {
+        if (it >= ids_base + 32) {
+            ids_base += 32;
+            my_ids = (ids_base + lane < n_my) ? bt[p0 + warp + (ids_base + lane) * AD_WARPS] : 0;
         }
-        at_cp_commit();
+        return __shfl_sync(0xffffffffu, my_ids, it - ids_base);
     };
-#pragma unroll
-    for (int s = 0; s < AD_STAGES - 1; ++s) issue(s);
-
-    for (int it = 0; it < n_my; ++it) {
-        issue(it + AD_STAGES - 1);
-        at_cp_wait<AD_STAGES - 1>();
-        __syncwarp();
-        const uint32_t st = pipe + (it % AD_STAGES) * AD_STAGE_BYTES;
-        float s[2][4];
-        at_qk_16keys(s, qf, st, lane);
-        // mask keys outside [lo, kvlen)
+    // One page: scores, online softmax, P.V. `qk` fills s[2][4] from the K tile, `pv` adds P.V from the V tile.
+    auto softmax_page = [&](float (&s)[2][4], int it, uint32_t (&pf)[4]) {
         const int key0 = (p0 + warp + it * AD_WARPS) * AD_PAGE + (lane & 3) * 2;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
@@ -99,7 +116,6 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
                 const int key = key0 + nt * 8 + (j & 1);
                 s[nt][j] = (key >= lo && key < kvlen) ? s[nt][j] * scale_log2 : -INFINITY;
             }
-        uint32_t pf[4];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {             // h = 0: row lane/4, h = 1: row lane/4 + 8
             float mx = fmaxf(fmaxf(s[0][2 * h], s[0][2 * h + 1]), fmaxf(s[1][2 * h], s[1][2 * h + 1]));
@@ -117,16 +133,107 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
             m[h] = mn;
             pf[h] = at_pack_bf16(p0v, p1v);       // keys 0-7 of this row
             pf[2 + h] = at_pack_bf16(p2v, p3v);   // keys 8-15
+            if (__any_sync(0xffffffffu, corr != 1.f)) {   // once the running maxima have settled nothing is rescaled
 #pragma unroll
-            for (int nt = 0; nt < AT_NT; ++nt) {
-                o[nt][2 * h] *= corr;
-                o[nt][2 * h + 1] *= corr;
+                for (int nt = 0; nt < AT_NT; ++nt) {
+                    o[nt][2 * h] *= corr;
+                    o[nt][2 * h + 1] *= corr;
+                }
             }
         }
-        at_pv_16keys(o, pf, st + AD_PAGE * AT_ROW_BYTES, lane);
+    };
+
+    if (AD_TMA_OK && use_tma) {
+        // ---- tensor copies into swizzled tiles, one mbarrier per warp and stage ----
+        const uint32_t pipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_TMA_STAGE_BYTES;
+        const uint32_t bars = (uint32_t)__cvta_generic_to_shared(smem) + AD_WARPS * AD_STAGES * AD_TMA_STAGE_BYTES + warp * AD_STAGES * 8;
+        if (lane == 0) {
+            for (int st = 0; st < AD_STAGES; ++st) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bars + st * 8));
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        }
         __syncwarp();
+        auto issue = [&](int it) {
+            if (it < n_my) {
+                const int page = page_of(it);
+                if (lane == 0) {
+                    const uint32_t st = pipe + (it % AD_STAGES) * AD_TMA_STAGE_BYTES, bar = bars + (it % AD_STAGES) * 8;
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the tile was read by ldmatrix before
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(AD_TMA_STAGE_BYTES) : "memory");
+                    const int rk = ((page * 2) * nkv + g) * AD_PAGE, rv = ((page * 2 + 1) * nkv + g) * AD_PAGE;
+#pragma unroll
+                    for (int bx = 0; bx < AD_BOXES; ++bx) {
+                        ad_tma_2d(st + bx * 2048, &kv_map, bx * 64, rk, bar);
+                        ad_tma_2d(st + (AD_BOXES + bx) * 2048, &kv_map, bx * 64, rv, bar);
+                    }
+                }
+            }
+        };
+#pragma unroll
+        for (int s = 0; s < AD_STAGES - 1; ++s) issue(s);
+        for (int it = 0; it < n_my; ++it) {
+            issue(it + AD_STAGES - 1);
+            if (!ad_mbar_wait(bars + (it % AD_STAGES) * 8, (it / AD_STAGES) & 1)) {
+                if (lane == 0) atomicExch(status, 21);
+                break;
+            }
+            const uint32_t kt = pipe + (it % AD_STAGES) * AD_TMA_STAGE_BYTES, vt = kt + AD_BOXES * 2048;
+            float s[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+            {
+                const int mat = lane >> 3, rr = lane & 7, key = (mat >> 1) * 8 + rr;
+#pragma unroll
+                for (int kk = 0; kk < AT_KSTEPS; ++kk) {
+                    uint32_t b0, b1, b2, b3;
+                    at_ldmatrix_x4(b0, b1, b2, b3, ad_swz(kt, key, kk * 2 + (mat & 1)));
+                    at_mma(s[0], qf[kk], b0, b1);
+                    at_mma(s[1], qf[kk], b2, b3);
+                }
+            }
+            uint32_t pf[4];
+            softmax_page(s, it, pf);
+            {
+                const int mat = lane >> 3, rr = lane & 7, key = (mat & 1) * 8 + rr;
+#pragma unroll
+                for (int nt = 0; nt < AT_NT; nt += 2) {
+                    uint32_t b0, b1, b2, b3;
+                    at_ldmatrix_x4_trans(b0, b1, b2, b3, ad_swz(vt, key, nt + (mat >> 1)));
+                    at_mma(o[nt], pf, b0, b1);
+                    at_mma(o[nt + 1], pf, b2, b3);
+                }
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---- per-lane asynchronous copies into padded tiles ----
+        const uint32_t pipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_STAGE_BYTES;
+        auto issue = [&](int it) {
+            if (it < n_my) {
+                const int page = page_of(it);
+                const uint32_t st = pipe + (it % AD_STAGES) * AD_STAGE_BYTES;
+                at_load_page(st, st + AD_PAGE * AT_ROW_BYTES, cache + (size_t)page * page_elems, g, nkv, AD_PAGE, 0, AD_PAGE, lane);
+            }
+            at_cp_commit();
+        };
+#pragma unroll
+        for (int s = 0; s < AD_STAGES - 1; ++s) issue(s);
+        for (int it = 0; it < n_my; ++it) {
+            issue(it + AD_STAGES - 1);
+            at_cp_wait<AD_STAGES - 1>();
+            __syncwarp();
+            const uint32_t st = pipe + (it % AD_STAGES) * AD_STAGE_BYTES;
+            float s[2][4];
+            at_qk_16keys(s, qf, st, lane);
+            uint32_t pf[4];
+            softmax_page(s, it, pf);
+            at_pv_16keys(o, pf, st + AD_PAGE * AT_ROW_BYTES, lane);
+            __syncwarp();
+        }
+        at_cp_wait<0>();
     }
-    at_cp_wait<0>();
     __syncthreads();                              // the pipeline memory is reused for the merge
 
     // merge the four warps: each writes (m, l, O) for its 16 rows
@@ -222,7 +329,10 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
 // Launches both kernels. Scratch: o_part float32 [n_decode*nh*n_splits*head_dim], ml_part [n_decode*nh*n_splits*2].
 static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
                      const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
-                     int n_splits, float* o_part, float* ml_part, cudaStream_t stream) {
+                     int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
+                     int* status = nullptr) {
+    static CUtensorMap no_map;                    // passed when there is no map: the kernel does not look at it
+    const int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
     static bool attr_set[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -235,7 +345,7 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     dim3 grid(n_splits, nkv * row_tiles, n_decode);
     IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, AD_SMEM, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
-        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part);
+        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, use_tma, status);
     const int n_rows = n_decode * nh;
     IL_LAUNCH(attn_decode_merge_kernel, (n_rows + 3) / 4, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window, pages_per_split,
                                                                   n_splits, (__nv_bfloat16*)out);
@@ -247,11 +357,39 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
 IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                              int bt_stride, const int* entry_kvlen, int page_size, int n_decode, int nh, int nkv, int hd,
                              float scale, int window, int pages_per_split, int n_splits, float* o_part, float* ml_part,
-                             cudaStream_t stream) {
+                             const void* kv_map, int* status, cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
     return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
-                     pages_per_split, n_splits, o_part, ml_part, stream);
+                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status);
+}
+
+// Writes a tensor map (128 bytes at `out_map`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16 seen as
+// rows of head_dim, for boxes of [16 rows x 64 columns] with the 128-byte swizzle. Returns 0, or IL_UNSUPPORTED.
+IL_EXPORT int il_attn_decode_kv_map(void* out_map, const void* cache, long long n_rows, int hd) {
+    if (!AD_TMA_OK || hd != HEAD_DIM || ((uintptr_t)cache & 15)) return IL_UNSUPPORTED;
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn enc = nullptr;
+    if (!enc) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            return IL_UNSUPPORTED;
+        enc = (encode_fn)p;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)n_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)AD_PAGE};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 2000 + (int)r;
+    memcpy(out_map, &m, sizeof(m));
+    return IL_OK;
 }

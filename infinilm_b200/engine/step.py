@@ -298,7 +298,7 @@ class StepRunner:
             grp = groups[g]
             if grp.need.kind == "paged_kv":
                 caches.append(PagedKVView(grp.storage[owner], view(s_bt[g]).view(Ep, widths[g]), self.cache.page_size,
-                                          writable=(owner == i), max_pages=widths[g]))
+                                          writable=(owner == i), max_pages=widths[g], tma_map=grp.tma_maps.get(owner)))
             else:
                 caches.append(StateView(grp.storage[owner], view(s_rs), view(s_wsl), writable=(owner == i)))
 

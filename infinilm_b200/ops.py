@@ -254,9 +254,10 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Opt
 def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      entry_kvlen: torch.Tensor, n_decode: int, page_size: int, n_heads: int, n_kv_heads: int,
                      head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
-                     o_part: torch.Tensor, ml_part: torch.Tensor) -> None:
+                     o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None) -> None:
     """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each).
     pages_per_split 0: each request's pages are divided evenly over the n_splits splits.
+    kv_map: the cache's tensor map from `kv_tensor_map` (pages then come in by TMA tensor copies).
     Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
     _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
@@ -271,11 +272,28 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_decode", "il_attn_decode", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                               _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void_p,
-                                              _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+    if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != 128):
+        raise KernelError("attention_decode: kv_map must be the 128-byte host tensor kv_tensor_map returned")
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
-             _ptr(o_part), _ptr(ml_part), _stream()), "attention_decode")
+             _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
+             _stream()), "attention_decode")
     count_launches(1)                             # the merge kernel
+
+
+def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:
+    """A TMA tensor map (128 bytes, on the host) of one layer's bfloat16 cache [pages,2,kv_heads,16,head_dim], or
+    None when the decode attention kernel has no tensor-copy path for this geometry (head_dim not a multiple of 64)."""
+    if not cache.is_cuda or cache.dtype != torch.bfloat16 or cache.dim() != 5 or cache.shape[3] != 16 or cache.shape[4] % 64:
+        return None
+    hd = cache.shape[4]
+    lib = build.load("attn_decode", {"HEAD_DIM": hd})
+    fn = lib.il_attn_decode_kv_map
+    fn.argtypes, fn.restype = [_c_void_p, _c_void_p, ctypes.c_longlong, _c_int], _c_int
+    m = torch.zeros(128, dtype=torch.uint8)
+    rc = fn(_c_void_p(m.data_ptr()), _ptr(cache), cache.numel() // hd, hd)
+    return m if rc == 0 else None
 
 
 def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,

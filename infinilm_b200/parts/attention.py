@@ -81,7 +81,7 @@ class Attention(Mixer):
     # else, and the whole float32 path, runs the plain kernel.
     FAST_PAGE = 16
     FAST_MAX_GROUP = 64
-    TARGET_BLOCKS = 2 * 148                       # blocks of the decode kernel that are resident at once (two per SM)
+    TARGET_BLOCKS = 2 * 148                       # blocks the decode splits aim at: more splits cost more in partials than they gain
 
     def attend(self, qkv, out, ctx, cache) -> None:
         G = self.nh // self.nkv
@@ -103,7 +103,7 @@ class Attention(Mixer):
             ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
                                  self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
                                  ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
-                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32))
+                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map)
         if E > n_dec:
             tpt = max(1, 64 // G)
             n_tiles = sum((q + tpt - 1) // tpt for q in ctx.h_qlen[n_dec:])

@@ -239,6 +239,16 @@ def test_attention_decode_bf16(cuda_device, nh, nkv, hd, window, splits):
     ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
                          window, pps, n_splits, o_part, ml_part)
     close(out.cpu(), c["ref"], "bfloat16")
+    # the same through TMA tensor copies of the pages, where the head size has that path
+    kv_map = ops.kv_tensor_map(c["cache"])
+    assert (kv_map is not None) == (hd % 64 == 0)
+    if kv_map is not None:
+        out.fill_(float("nan"))
+        ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
+                             window, pps, n_splits, o_part, ml_part, kv_map=kv_map)
+        torch.cuda.synchronize()
+        assert int(ops.stream_status("cuda:0").item()) == 0
+        close(out.cpu(), c["ref"], "bfloat16")
     # pages_per_split 0: every request divides its own pages evenly over the splits
     out.fill_(float("nan"))
     o_part = torch.full((E * nh * splits * hd,), float("nan"), device="cuda")
