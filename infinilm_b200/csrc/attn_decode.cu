@@ -7,7 +7,8 @@
 //   copies (STAGES pages in flight), computes S = Q.K^T (f32), an online softmax in f32 (base 2,
 //   scale folded in), and O += P.V with P rounded to bfloat16. The four warps merge in shared
 //   memory and the block writes one partial (O unnormalised, running max, sum) per split.
-//   il_attn_decode_merge combines the partials of a (token, head) and writes bfloat16 output.
+//   The block that finishes last among the splits of a (request, kv head) merges their partials and writes the
+//   bfloat16 output (found with a counter, no block waits); without a counter array a second kernel merges.
 //
 // Token t (= entry t; decode entries come first in a step) has kv length entry_kvlen[t]; its query
 // sits at position kvlen-1 and sees positions max(0, kvlen-window) .. kvlen-1 (window <= 0: all).
@@ -52,11 +53,49 @@ __device__ __forceinline__ uint32_t ad_swz(uint32_t block, int r, int ch) {
     return block + (ch >> 3) * 2048 + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
 }
 
+constexpr int AD_MAX_SPLITS = 128;
+
+// One warp merges the splits of one (token, head) row: the split factors exp2(m_s - M) are computed once (lanes over
+// splits) and kept in `fs` (shared memory, AD_MAX_SPLITS floats of this warp); then each lane sums four output columns.
+__device__ __forceinline__ void ad_merge_row(float* fs, const float* __restrict__ o_part, const float* __restrict__ ml_part,
+                                             size_t row, int n_valid, int n_splits, __nv_bfloat16* __restrict__ out, int lane) {
+    const size_t pr0 = row * n_splits;
+    float M = -INFINITY;
+    for (int s = lane; s < n_valid; s += 32) M = fmaxf(M, ml_part[(pr0 + s) * 2]);
+    M = il_warp_max(M);
+    float L = 0.f;
+    for (int s = lane; s < n_valid; s += 32) {
+        const float ms = ml_part[(pr0 + s) * 2];
+        const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+        fs[s] = f;
+        L += f * ml_part[(pr0 + s) * 2 + 1];
+    }
+    L = il_warp_sum(L);
+    __syncwarp();
+    const float inv = 1.f / L;
+    for (int d = lane * 4; d < AT_HD; d += 128) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+        for (int s = 0; s < n_valid; ++s) {
+            const float4 v = *reinterpret_cast<const float4*>(o_part + (pr0 + s) * AT_HD + d);
+            const float f = fs[s];
+            acc.x += f * v.x;
+            acc.y += f * v.y;
+            acc.z += f * v.z;
+            acc.w += f * v.w;
+        }
+        const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(out + row * AT_HD + d) = make_uint2(a, b);
+    }
+    __syncwarp();
+}
+
 __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const __nv_bfloat16* __restrict__ qkv, int row_stride, const __nv_bfloat16* __restrict__ cache,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
-    float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, int use_tma, int* __restrict__ status) {
+    float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, int use_tma, int* __restrict__ status,
+    int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     il_pdl_launch_dependents();
@@ -274,12 +313,31 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
             ml_part[pr * 2 + 1] = L;
         }
     }
+    if (!counters) return;                        // the merge runs as a kernel of its own
+
+    // The block that finishes last among the splits of this (request, kv head, row tile) merges them. Every block
+    // makes its partials visible (fence), then takes a ticket; the last ticket holder sees all partials. It puts
+    // the counter back to zero for the next launch. No block waits for another.
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    const int n_valid = min(n_splits, (last_page - first_page + pages_per_split) / pages_per_split);
+    if (threadIdx.x == 0) {
+        int* cnt = counters + ((size_t)e * nkv + g) * row_tiles + rt;
+        const int ticket = atomicAdd(cnt, 1);
+        s_last = (ticket == n_valid - 1);
+        if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float* fs = reinterpret_cast<float*>(smem) + (size_t)warp * AD_MAX_SPLITS;    // the warps' partial tiles are done with
+    for (int r = warp; r < rows_valid; r += AD_WARPS)
+        ad_merge_row(fs, o_part, ml_part, (size_t)e * nh + head0 + r, n_valid, n_splits, out, lane);
 }
 
-constexpr int AD_MAX_SPLITS = 128;
-
-// One warp per (token, head): the split factors exp2(m_s - M) are computed once (lanes over splits)
-// and kept in shared memory; then each lane sums four output columns over the splits.
+// The merge as a kernel of its own (one warp per (token, head)), for callers that do not give the attention kernel
+// a counter array to find its last block with.
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                                                                 const int* __restrict__ entry_kvlen, int nh, int n_rows, int window,
                                                                 int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out) {
@@ -296,41 +354,14 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
     if (pages_per_split <= 0) pages_per_split = (n_pages + n_splits - 1) / n_splits;
     int n_valid = (n_pages + pages_per_split - 1) / pages_per_split;
     if (n_valid > n_splits) n_valid = n_splits;
-    const size_t pr0 = (size_t)row * n_splits;
-    float M = -INFINITY;
-    for (int s = lane; s < n_valid; s += 32) M = fmaxf(M, ml_part[(pr0 + s) * 2]);
-    M = il_warp_max(M);
-    float L = 0.f;
-    for (int s = lane; s < n_valid; s += 32) {
-        const float ms = ml_part[(pr0 + s) * 2];
-        const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-        fs[warp][s] = f;
-        L += f * ml_part[(pr0 + s) * 2 + 1];
-    }
-    L = il_warp_sum(L);
-    __syncwarp();
-    const float inv = 1.f / L;
-    for (int d = lane * 4; d < AT_HD; d += 128) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int s = 0; s < n_valid; ++s) {
-            const float4 v = *reinterpret_cast<const float4*>(o_part + (pr0 + s) * AT_HD + d);
-            const float f = fs[warp][s];
-            acc.x += f * v.x;
-            acc.y += f * v.y;
-            acc.z += f * v.z;
-            acc.w += f * v.w;
-        }
-        const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
-        *reinterpret_cast<uint2*>(out + (size_t)row * AT_HD + d) = make_uint2(a, b);
-    }
+    ad_merge_row(fs[warp], o_part, ml_part, (size_t)row, n_valid, n_splits, out, lane);
 }
 
 // Launches both kernels. Scratch: o_part float32 [n_decode*nh*n_splits*head_dim], ml_part [n_decode*nh*n_splits*2].
 static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
                      const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
                      int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
-                     int* status = nullptr) {
+                     int* status = nullptr, int* counters = nullptr) {
     static CUtensorMap no_map;                    // passed when there is no map: the kernel does not look at it
     const int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
     static bool attr_set[64];
@@ -345,7 +376,8 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     dim3 grid(n_splits, nkv * row_tiles, n_decode);
     IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, AD_SMEM, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
-        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, use_tma, status);
+        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, use_tma, status, counters, (__nv_bfloat16*)out);
+    if (counters) return IL_OK;                   // merged by the last block of each group of splits
     const int n_rows = n_decode * nh;
     IL_LAUNCH(attn_decode_merge_kernel, (n_rows + 3) / 4, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window, pages_per_split,
                                                                   n_splits, (__nv_bfloat16*)out);
@@ -357,13 +389,13 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
 IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                              int bt_stride, const int* entry_kvlen, int page_size, int n_decode, int nh, int nkv, int hd,
                              float scale, int window, int pages_per_split, int n_splits, float* o_part, float* ml_part,
-                             const void* kv_map, int* status, cudaStream_t stream) {
+                             const void* kv_map, int* status, int* counters, cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
     return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
-                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status);
+                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, counters);
 }
 
 // Writes a tensor map (128 bytes at `out_map`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16 seen as

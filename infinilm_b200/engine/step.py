@@ -61,13 +61,14 @@ class Workspace:
             self._bufs[key] = buf
         return buf[:n]
 
-    def flat(self, tag: str, n: int, dtype: torch.dtype) -> torch.Tensor:
+    def flat(self, tag: str, n: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """`zero`: the buffer is zero when it is made (its users leave it zero)."""
         key = (tag, "flat", dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < n:
             if buf is not None:
                 self.version += 1
-            buf = torch.empty(max(n, 1024), dtype=dtype, device=self.device)
+            buf = (torch.zeros if zero else torch.empty)(max(n, 1024), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:n]
 

@@ -254,10 +254,13 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Opt
 def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      entry_kvlen: torch.Tensor, n_decode: int, page_size: int, n_heads: int, n_kv_heads: int,
                      head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
-                     o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None) -> None:
+                     o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None,
+                     counters: Optional[torch.Tensor] = None) -> None:
     """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each).
     pages_per_split 0: each request's pages are divided evenly over the n_splits splits.
     kv_map: the cache's tensor map from `kv_tensor_map` (pages then come in by TMA tensor copies).
+    counters: int32 zeros, one per (row, kv head, tile of 16 query heads); with it the last block of each group of
+    splits merges them (the kernel leaves the counters at zero), without it a second kernel does.
     Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
     _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
@@ -272,14 +275,19 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_decode", "il_attn_decode", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                               _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void_p,
-                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+    if counters is not None:
+        n_cnt = n_decode * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
+        if not counters.is_cuda or counters.dtype != torch.int32 or counters.numel() < n_cnt:
+            raise KernelError("attention_decode: counters must be int32 on the device, one per (row, kv head, head tile)")
     if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != 128):
         raise KernelError("attention_decode: kv_map must be the 128-byte host tensor kv_tensor_map returned")
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
-             _stream()), "attention_decode")
-    count_launches(1)                             # the merge kernel
+             _ptr(counters), _stream()), "attention_decode")
+    if counters is None:
+        count_launches(1)                         # the merge kernel
 
 
 def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:

@@ -104,6 +104,8 @@ class Attention(Mixer):
                                  self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
                                  ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
                                  ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map)
+            # (the kernel can also merge the splits itself, in the last block of each group - `counters=` - but the
+            # merge as a second, wide launch measured faster: 3.7 against 3.9 ms for the 8B decode step at batch 8)
         if E > n_dec:
             tpt = max(1, 64 // G)
             n_tiles = sum((q + tpt - 1) // tpt for q in ctx.h_qlen[n_dec:])

@@ -249,6 +249,15 @@ def test_attention_decode_bf16(cuda_device, nh, nkv, hd, window, splits):
         torch.cuda.synchronize()
         assert int(ops.stream_status("cuda:0").item()) == 0
         close(out.cpu(), c["ref"], "bfloat16")
+    # merged by the last block of each group of splits (a counter finds it) instead of a second kernel; twice, since
+    # the kernel has to leave the counters at zero
+    counters = torch.zeros(E * nkv * ((nh // nkv + 15) // 16), dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        out.fill_(float("nan"))
+        ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
+                             window, pps, n_splits, o_part, ml_part, kv_map=kv_map, counters=counters)
+        close(out.cpu(), c["ref"], "bfloat16")
+        assert int(counters.abs().sum()) == 0
     # pages_per_split 0: every request divides its own pages evenly over the splits
     out.fill_(float("nan"))
     o_part = torch.full((E * nh * splits * hd,), float("nan"), device="cuda")
