@@ -153,6 +153,64 @@ def profile_step(args) -> int:
     return 0
 
 
+CONFIG_05B = dict(CONFIG_8B, num_hidden_layers=24, hidden_size=1024, num_attention_heads=16, num_key_value_heads=2, head_dim=64,
+                  intermediate_size=4096, tie_word_embeddings=True,
+                  rope_scaling={"rope_type": "longrope", "short_factor": [1.0 + 0.05 * i for i in range(32)],
+                                "long_factor": [1.0 + 0.25 * i for i in range(32)], "original_max_position_embeddings": 32768})
+
+
+def run_workload(args) -> int:
+    """The two serving workloads of the baseline beside the headline: both go through `LLM.generate`
+    (scheduler, chunked prefill mixed with decoding, paged cache, sampling), host tokens in and out."""
+    import torch
+
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.llm import LLM, SamplingParams
+    from infinilm_b200.weights import random_tensors
+    long_ctx = args.workload == "long_context"
+    raw = dict(CONFIG_8B if long_ctx else CONFIG_05B)
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    cfg = config_from_json(raw)
+    g = torch.Generator().manual_seed(2)
+    if long_ctx:
+        n_req, new = 8, 512
+        lens = [16384] * n_req
+        max_b, chunk, budget = 8, 2048, 2048 + 8
+    else:
+        n_req, new = 256, 256
+        lens = torch.randint(16, 4097, (n_req,), generator=g).tolist()
+        max_b, chunk, budget = 256, 2048, 4096
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    pages = sum((n + new + PAGE - 1) // PAGE + 1 for n in lens) + 16
+    t0 = time.perf_counter()
+    llm = LLM.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", num_blocks=pages, block_size=PAGE,
+                           max_batch_size=max_b, max_num_batched_tokens=budget, chunk_size=chunk, enable_graph=not args.no_graph)
+    sp = SamplingParams(top_k=1, max_tokens=new, ignore_eos=True)
+    warm = llm.generate(prompt_token_ids=[prompts[0][:64]], sampling_params=SamplingParams(top_k=1, max_tokens=4, ignore_eos=True))
+    assert len(warm[0].outputs[0].token_ids) == 4
+    torch.cuda.synchronize()
+    steps0, toks0 = llm.engine.runner.steps_run, llm.engine.runner.tokens_run
+    t1 = time.perf_counter()
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=sp)
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    n_new = sum(len(o.outputs[0].token_ids) for o in outs)
+    assert n_new == n_req * new and all(o.finish_reason.value == "length" for o in outs)
+    st = llm.stats()
+    rec = {"workload": args.workload, "impl": "ours", "dtype": "bf16", "n_gpus": 1,
+           "config": {"model": "MiniCPM4-8B sizes" if long_ctx else "MiniCPM4-0.5B sizes", "layers": cfg.num_hidden_layers,
+                      "requests": n_req, "prompt_tokens": sum(lens), "new_tokens_each": new, "chunk": chunk, "page_size": PAGE,
+                      "max_live": max_b, "token_budget": budget},
+           "seconds": t2 - t1, "steps": llm.engine.runner.steps_run - steps0,
+           "tokens_run": llm.engine.runner.tokens_run - toks0,
+           "total_tok_per_s": (sum(lens) + n_new) / (t2 - t1), "new_tok_per_s": n_new / (t2 - t1),
+           "preemptions": st["preemptions"], "free_pages_after": st["free_pages"], "pool_pages": st["pool_pages"],
+           "setup_s": round(t1 - t0, 1)}
+    print(json.dumps(rec))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -164,6 +222,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
     ap.add_argument("--points", type=str, default="1,64", help="batch sizes of the extra decode points")
+    ap.add_argument("--workload", choices=["default", "long_context", "continuous"], default="default",
+                    help="default: the benchmark line. long_context: 8 requests x 16,384-token prompts at 8B sizes, prompt "
+                         "portions of 2,048 interleaved with the others' decoding, 512 new tokens each. continuous: 256 requests "
+                         "at 0.5B sizes, prompts of 16..4096 tokens, 256 new tokens each. Both print their own JSON line.")
     ap.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
                     help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off); "
                          "use with --layers 2 to keep the capture small")
@@ -190,6 +252,8 @@ def main() -> int:
 
     if args.profile_step:
         return profile_step(args)
+    if args.workload != "default":
+        return run_workload(args)
     raw = dict(CONFIG_8B)
     full_layers = raw["num_hidden_layers"]
     n_layers = args.layers or full_layers

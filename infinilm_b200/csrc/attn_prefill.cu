@@ -21,6 +21,13 @@ constexpr int AP_STAGE_BYTES = AP_TILE_PAGES * AP_PAGE_BYTES;
 constexpr int AP_STAGES = 2;
 constexpr int AP_SMEM = AP_STAGES * AP_STAGE_BYTES;
 
+// 2^x on the special-function unit (ex2.approx: -inf gives 0, relative error about 2^-22).
+__device__ __forceinline__ float ap_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
     const __nv_bfloat16* __restrict__ qkv, int row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
@@ -82,10 +89,14 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
     // warp-wide and block-wide key ranges
     int wmax = max(rpos[0], rpos[1]);
     int wmin_lo = min(rvalid[0] ? rlo[0] : 0x7fffffff, rvalid[1] ? rlo[1] : 0x7fffffff);
+    int wmin_pos = min(rpos[0], rpos[1]);         // -1 when a row of the warp is not valid: such a warp always masks
+    int wmax_lo = max(rlo[0], rlo[1]);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
         wmax = max(wmax, __shfl_xor_sync(0xffffffffu, wmax, off));
         wmin_lo = min(wmin_lo, __shfl_xor_sync(0xffffffffu, wmin_lo, off));
+        wmin_pos = min(wmin_pos, __shfl_xor_sync(0xffffffffu, wmin_pos, off));
+        wmax_lo = max(wmax_lo, __shfl_xor_sync(0xffffffffu, wmax_lo, off));
     }
     const int bpos_first = start_pos + (tok0 - q0), bpos_last = bpos_first + n_tok - 1;
     const int blo = (window > 0 && bpos_first - window + 1 > 0) ? bpos_first - window + 1 : 0;
@@ -146,19 +157,23 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
                 }
             }
         }
+        // Masks only where a key can lie outside a row's range: above the warp's lowest query position, or below
+        // its highest window edge. Scores stay unscaled here; the scale goes into the exponent below.
 #pragma unroll
         for (int p = 0; p < AP_TILE_PAGES; ++p) {
             if (!use[p]) continue;
             const int k0 = key_base + p * AP_PAGE;
+            const bool need_mask = (k0 + AP_PAGE - 1 > wmin_pos) || (k0 < wmax_lo);
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int key = k0 + nt * 8 + (lane & 3) * 2 + (j & 1);
                     const int h = j >> 1;
-                    const float v = (key <= rpos[h] && key >= rlo[h]) ? s[p][nt][j] * scale_log2 : -INFINITY;
-                    s[p][nt][j] = v;
-                    mx[h] = fmaxf(mx[h], v);
+                    if (need_mask) {
+                        const int key = k0 + nt * 8 + (lane & 3) * 2 + (j & 1);
+                        if (!(key <= rpos[h] && key >= rlo[h])) s[p][nt][j] = -INFINITY;
+                    }
+                    mx[h] = fmaxf(mx[h], s[p][nt][j]);
                 }
         }
         float corr[2], msafe[2];
@@ -166,17 +181,19 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
         for (int h = 0; h < 2; ++h) {
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-            const float mn = fmaxf(m[h], mx[h]);
-            corr[h] = (mn == -INFINITY) ? 1.f : exp2f(m[h] - mn);
+            const float mn = fmaxf(m[h], mx[h] * scale_log2);      // running maximum of the scaled scores (scale > 0)
+            corr[h] = (mn == -INFINITY) ? 1.f : ap_ex2(m[h] - mn);
             msafe[h] = (mn == -INFINITY) ? 0.f : mn;
             m[h] = mn;
         }
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {   // nothing to rescale once the maxima have settled
 #pragma unroll
-        for (int nt = 0; nt < AT_NT; ++nt) {
-            o[nt][0] *= corr[0];
-            o[nt][1] *= corr[0];
-            o[nt][2] *= corr[1];
-            o[nt][3] *= corr[1];
+            for (int nt = 0; nt < AT_NT; ++nt) {
+                o[nt][0] *= corr[0];
+                o[nt][1] *= corr[0];
+                o[nt][2] *= corr[1];
+                o[nt][3] *= corr[1];
+            }
         }
         float rs[2] = {0.f, 0.f};
 #pragma unroll
@@ -185,8 +202,9 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
             uint32_t pf[4];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const float a = exp2f(s[p][0][2 * h] - msafe[h]), b = exp2f(s[p][0][2 * h + 1] - msafe[h]);
-                const float c = exp2f(s[p][1][2 * h] - msafe[h]), d = exp2f(s[p][1][2 * h + 1] - msafe[h]);
+                // 2^(s * scale - m) with one fused multiply-add per score
+                const float a = ap_ex2(fmaf(s[p][0][2 * h], scale_log2, -msafe[h])), b = ap_ex2(fmaf(s[p][0][2 * h + 1], scale_log2, -msafe[h]));
+                const float c = ap_ex2(fmaf(s[p][1][2 * h], scale_log2, -msafe[h])), d = ap_ex2(fmaf(s[p][1][2 * h + 1], scale_log2, -msafe[h]));
                 rs[h] += a + b + c + d;
                 pf[h] = at_pack_bf16(a, b);
                 pf[2 + h] = at_pack_bf16(c, d);

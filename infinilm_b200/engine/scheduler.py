@@ -49,7 +49,7 @@ class FinishReason(enum.Enum):
     ABORTED = "aborted"
 
 
-@dataclass
+@dataclass(eq=False)                              # a request is itself: compared and hashed by identity
 class Request:
     request_id: str
     prompt_token_ids: List[int]
@@ -69,6 +69,19 @@ class Request:
     @property
     def all_token_ids(self) -> List[int]:
         return self.prompt_token_ids + self.output_token_ids
+
+    @property
+    def n_tokens(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+    def tokens_from(self, start: int, n: int) -> List[int]:
+        """Tokens start .. start+n of prompt followed by output, without joining the two lists."""
+        np_ = len(self.prompt_token_ids)
+        if start + n <= np_:
+            return self.prompt_token_ids[start: start + n]
+        if start >= np_:
+            return self.output_token_ids[start - np_: start - np_ + n]
+        return self.prompt_token_ids[start:] + self.output_token_ids[: start + n - np_]
 
     @property
     def n_cached(self) -> int:
@@ -179,10 +192,9 @@ class Scheduler:
     def _next_tokens(self, r: Request, budget: int) -> List[int]:
         """The tokens `r` would run next: one if it is decoding, else a portion of what is not
         yet in the cache (prompt, and after a preemption also the tokens already produced)."""
-        all_ids = r.all_token_ids
-        left = len(all_ids) - r.n_cached
+        left = r.n_tokens - r.n_cached
         n = min(left, self.chunk_size, budget)
-        return all_ids[r.n_cached: r.n_cached + n]
+        return r.tokens_from(r.n_cached, n)
 
     def _preempt_youngest(self, out: SchedulerOutput, keep: Request) -> bool:
         """Gives back the pages of the youngest running request other than `keep` that is not
@@ -213,8 +225,8 @@ class Scheduler:
             return need if need <= free else -1
 
         # 1. running requests, decoding ones first (one token each), then unfinished prompts, oldest first
-        decoding = [r for r in self.running if not r.closing and len(r.all_token_ids) - r.n_cached == 1]
-        filling = [r for r in self.running if not r.closing and len(r.all_token_ids) - r.n_cached > 1]
+        decoding = [r for r in self.running if not r.closing and r.n_tokens - r.n_cached == 1]
+        filling = [r for r in self.running if not r.closing and r.n_tokens - r.n_cached > 1]
         for r in sorted(decoding, key=lambda r: r.arrival) + sorted(filling, key=lambda r: r.arrival):
             if r not in self.running:             # preempted a moment ago
                 continue
@@ -234,7 +246,7 @@ class Scheduler:
                 continue                           # waits for pages; an older request will free some
             free -= need
             budget -= len(toks)
-            out.entries.append(ScheduledEntry(r, toks, samples=(r.n_cached + len(toks) == len(r.all_token_ids))))
+            out.entries.append(ScheduledEntry(r, toks, samples=(r.n_cached + len(toks) == r.n_tokens)))
 
         # 2. admissions, in arrival order; the first that does not fit stops the scan
         while self.waiting and budget > 0 and len(self.running) < self.max_batch_size:
@@ -256,7 +268,7 @@ class Scheduler:
             self.running.append(r)
             free -= need
             budget -= len(toks)
-            out.entries.append(ScheduledEntry(r, toks, samples=(len(toks) == len(r.all_token_ids))))
+            out.entries.append(ScheduledEntry(r, toks, samples=(len(toks) == r.n_tokens)))
         return out
 
     # -- after the step ----------------------------------------------------------------------
@@ -283,7 +295,7 @@ class Scheduler:
             r.last_sample_row = row
             row += 1
             if len(r.output_token_ids) >= r.params.max_tokens or (
-                    self.max_model_len is not None and len(r.all_token_ids) >= self.max_model_len):
+                    self.max_model_len is not None and r.n_tokens >= self.max_model_len):
                 r.closing = True
 
     def retire(self, out: SchedulerOutput, sampled: Sequence[int]) -> List[Request]:

@@ -117,7 +117,7 @@ class StepRunner:
         """A pinned host buffer (one of a small ring, so the copy of an earlier step is never
         overwritten while in flight) and the device buffer the kernels read."""
         if self._desc_dev is None or self._desc_dev.numel() < n_ints:
-            cap = max(n_ints, 1 << 16)
+            cap = max(2 * n_ints, 1 << 16)          # grown with headroom: pinned allocations are slow
             if self._desc_dev is not None:
                 torch.cuda.current_stream(self.device).synchronize()
             self._desc_ring = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(4)]
