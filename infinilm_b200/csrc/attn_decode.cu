@@ -98,8 +98,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    il_pdl_launch_dependents();
-    il_pdl_wait();
+    il_pdl_begin();
     const int split = blockIdx.x;
     const int G = nh / nkv;
     const int row_tiles = (G + 15) / 16;
@@ -291,6 +290,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
             row[nt * 8 + (lane & 3) * 2 + 1] = o[nt][2 * h + 1];
         }
     }
+    il_pdl_tail();
     __syncthreads();
     const float* all = reinterpret_cast<const float*>(smem);
     for (int idx = threadIdx.x; idx < rows_valid * AT_HD; idx += AD_WARPS * 32) {
@@ -342,8 +342,7 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __r
                                                                 const int* __restrict__ entry_kvlen, int nh, int n_rows, int window,
                                                                 int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out) {
     __shared__ float fs[4][AD_MAX_SPLITS];
-    il_pdl_launch_dependents();
-    il_pdl_wait();
+    il_pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp;        // = e * nh + head
     if (row >= n_rows) return;

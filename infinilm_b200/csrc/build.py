@@ -99,8 +99,14 @@ def _key(src_path: str, defines: Tuple[Tuple[str, str], ...], extra: Tuple[str, 
     return h.hexdigest()[:16]
 
 
+def _env_flags() -> Tuple[str, ...]:
+    """Further nvcc flags from INFINILM_B200_NVCC_FLAGS (space separated); they are part of a library's key."""
+    return tuple(os.environ.get("INFINILM_B200_NVCC_FLAGS", "").split())
+
+
 def so_path(name: str, defines: Optional[Dict[str, object]] = None,
             extra_flags: Tuple[str, ...] = ()) -> str:
+    extra_flags = tuple(extra_flags) + _env_flags()
     dfs = tuple(sorted((k, str(v)) for k, v in (defines or {}).items()))
     src = os.path.join(_HERE, name + ".cu")
     tag = "".join(f"-{k}{v}" for k, v in dfs)
@@ -119,7 +125,7 @@ def compile_source(name: str, defines: Optional[Dict[str, object]] = None,
     nvcc = find_nvcc()
     dfs = [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [nvcc] + ARCH_FLAGS + BASE_FLAGS + list(extra_flags) + dfs + ["-I", _HERE, "-o", tmp, src]
+    cmd = [nvcc] + ARCH_FLAGS + BASE_FLAGS + list(extra_flags) + list(_env_flags()) + dfs + ["-I", _HERE, "-o", tmp, src]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

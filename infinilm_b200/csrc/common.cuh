@@ -68,21 +68,33 @@ __device__ __forceinline__ float il_block_max(float v, float* sh) {
 }
 
 // ---- programmatic dependent launch --------------------------------------------------------------
-// Kernels of the decode path can be launched so that the next kernel in the stream may become
-// resident while this one still runs (set INFINILM_B200_PDL=1; off by default: on the 8B decode
-// step it measured slower, 6.2 ms against 3.7 ms a step, with every kernel letting its successor
-// start at once). A kernel lets its successor start early (il_pdl_launch_dependents) and waits for
-// its predecessor to have finished and flushed (il_pdl_wait) before it touches anything another
-// kernel produces or reads. Both are no-ops in a kernel that was launched the ordinary way.
+// Kernels of the decode path are launched so that the next kernel in the stream may become resident
+// while this one drains (INFINILM_B200_PDL=0 turns it off). A kernel waits for its predecessor to have
+// finished and flushed (il_pdl_begin) before it touches anything another kernel produces or reads, and
+// lets its successor in once its main loop is over (il_pdl_tail; a kernel without one does so by ending).
+// Both are no-ops in a kernel that was launched the ordinary way. Measured on the 8B decode step at
+// batch 8: 3.65 ms so, 3.70 ms without; with every kernel letting its successor in at its very start
+// (IL_PDL_MODE 0) 6.7 ms, because waiting blocks of later kernels then crowd the SMs.
 __device__ __forceinline__ void il_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void il_pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+// Where a kernel lets its successor in: IL_PDL_MODE 0 at its start, 1 after its main loop, 2 only by ending.
+#ifndef IL_PDL_MODE
+#define IL_PDL_MODE 1
+#endif
+__device__ __forceinline__ void il_pdl_begin() {
+    if (IL_PDL_MODE == 0) il_pdl_launch_dependents();
+    il_pdl_wait();
+}
+__device__ __forceinline__ void il_pdl_tail() {
+    if (IL_PDL_MODE == 1) il_pdl_launch_dependents();
+}
 
 #include <cstdlib>
 static inline bool il_pdl_enabled() {
     static int on = -1;
     if (on < 0) {
         const char* e = getenv("INFINILM_B200_PDL");
-        on = (e && e[0] == '1') ? 1 : 0;
+        on = (e && e[0] == '0') ? 0 : 1;
     }
     return on == 1;
 }

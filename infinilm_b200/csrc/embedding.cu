@@ -6,8 +6,7 @@
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float scale,
                              float* __restrict__ out, int H, int V, int round_bf16) {
-    il_pdl_launch_dependents();
-    il_pdl_wait();
+    il_pdl_begin();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -42,8 +41,7 @@ IL_EXPORT int il_embed(const int* ids, const void* table, int table_kind, float 
 // into the next step's token list. Out-of-vocabulary values are caught by the gather above.
 __global__ void patch_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ rows, const int* __restrict__ src_idx,
                                     const int* __restrict__ src, int n) {
-    il_pdl_launch_dependents();
-    il_pdl_wait();
+    il_pdl_begin();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) token_ids[rows[i]] = src[src_idx[i]];
 }

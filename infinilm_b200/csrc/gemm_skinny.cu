@@ -49,8 +49,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_skinny_kernel(const __nv_b
             if (n > N - 1) n = N - 1;             // rows past the end are computed and dropped
             wrow[s][h] = W + ((size_t)(GLU ? h : 0) * N + n) * ldw;
         }
-    il_pdl_launch_dependents();
-    il_pdl_wait();
+    il_pdl_begin();
     const __nv_bfloat16* xrow[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) xrow[t] = (t * 8 + r < M) ? x + (size_t)(t * 8 + r) * ldx : nullptr;
@@ -89,6 +88,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32) gemm_skinny_kernel(const __nv_b
                     gs_mma(acc[s][t], a[u][s][0].z, a[u][s][1].z, a[u][s][0].w, a[u][s][1].w, b[u][t].z, b[u][t].w);
                 }
     }
+    il_pdl_tail();
 #pragma unroll
     for (int s = 0; s < NW; ++s)
 #pragma unroll

@@ -53,8 +53,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict_
                                                               const void* __restrict__ w, int w_kind, float eps, TA* __restrict__ out,
                                                               const int* __restrict__ rows, int H) {
     __shared__ float red[32];
-    il_pdl_launch_dependents();
-    il_pdl_wait();
+    il_pdl_begin();
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
     float* rr = resid + (size_t)r * H;

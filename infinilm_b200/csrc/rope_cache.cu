@@ -17,8 +17,7 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const in
                                   const int* __restrict__ tok_entry, const int* __restrict__ block_table,
                                   int bt_stride, TA* __restrict__ cache, int page_size, int nh, int nkv, int hd,
                                   int rot, const float* __restrict__ inv_freq, float mscale) {
-    il_pdl_launch_dependents();
-    il_pdl_wait();
+    il_pdl_begin();
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     TA* row = qkv + (size_t)t * row_stride;

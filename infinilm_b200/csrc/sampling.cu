@@ -37,8 +37,7 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
     __shared__ int shi[32];
     __shared__ float s_prefix[SP_THREADS];
     __shared__ int s_result;
-    il_pdl_launch_dependents();
-    il_pdl_wait();
+    il_pdl_begin();
     const int r = blockIdx.x, tid = threadIdx.x;
     const float* row = logits + (size_t)r * ld;
 
