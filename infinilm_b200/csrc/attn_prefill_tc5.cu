@@ -1,0 +1,339 @@
+// Prefill attention over the paged cache on the 5th-generation tensor cores (head_dim 64 or 128, bfloat16):
+// prompt portions of any length, each token attending causally (and inside its window) to what its request
+// has in the cache, earlier steps' keys and this step's own.
+//
+//   A block owns up to 128 rows: TPT consecutive tokens of one entry times the G query heads of one kv head
+//   (row r -> token r / G, head r % G), and walks the keys in tiles of 64 (four pages of 16).
+//     S = Q.K^T   tcgen05.mma, M 128, N 64, both operands in shared memory (K-major, 128-byte swizzle): Q is put
+//                 there once by the softmax threads, K pages arrive as TMA tensor copies. S lives in tensor memory,
+//                 two buffers, so the product of tile j+1 runs while tile j is in the softmax.
+//     softmax     four warps, one thread a row: tcgen05.ld of the row's 64 scores, mask where the tile touches the
+//                 row's causal or window edge, base-2 exponent with the scale folded in, f32 sum. The running
+//                 maximum is raised only when a tile's maximum is more than 2^8 above it; then the row of O is
+//                 rescaled in tensor memory. P goes back to tensor memory as bfloat16, over its own scores.
+//     O += P.V    tcgen05.mma, M 128, N head_dim, A = P from tensor memory, B = the V pages as they lie in the
+//                 cache (keys by head_dim: MN-major); O accumulates in tensor memory and is divided by the row
+//                 sums at the end.
+//   Roles by warp: 0 producer (TMA, a ring of two K/V stages), 1 tensor-core issue and tensor-memory allocation,
+//   2-5 softmax and output. 256 columns of tensor memory and about 98 KB of shared memory: two blocks per SM.
+//
+//   Pages past the entry's last page are read as the last page again (finite values the mask removes).
+//   Every mbarrier wait is bounded; one that runs out sets *status and all roles leave their loops.
+//
+//   grid (tiles, kv heads). Tiles are numbered over the entries [first_entry, n_entries) in order; a block finds
+//   its entry by walking entry_qstart.
+#include "tcgen05.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=64 or 128"
+#endif
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tensor-memory prefill kernel takes head_dim 64 or 128");
+
+constexpr int PT_HD = HEAD_DIM;
+constexpr int PT_HALVES = HEAD_DIM / 64;          // 128-byte column blocks of a row
+constexpr int PT_ROWS = 128;
+constexpr int PT_KEYS = 64;
+constexpr int PT_PAGE = 16;
+constexpr int PT_TILE_PAGES = PT_KEYS / PT_PAGE;
+constexpr int PT_STAGES = 2;
+constexpr int PT_Q_HALF = PT_ROWS * 128;          // bytes of one column block of Q
+constexpr int PT_Q_BYTES = PT_HALVES * PT_Q_HALF;
+constexpr int PT_K_HALF = PT_KEYS * 128;
+constexpr int PT_K_BYTES = PT_HALVES * PT_K_HALF; // K tile; the V tile has the same size
+constexpr int PT_STAGE_BYTES = 2 * PT_K_BYTES;
+constexpr int PT_THREADS = 192;
+constexpr int PT_TMEM_COLS = 256;
+constexpr int PT_COL_O = 2 * PT_KEYS;             // S buffers at columns 0 and 64, O behind them
+constexpr int PT_N_BARS = 1 + 3 * PT_STAGES + 2 + 2 + 1;
+constexpr int PT_SMEM = 1024 + PT_Q_BYTES + PT_STAGES * PT_STAGE_BYTES + PT_N_BARS * 8 + 16;
+constexpr unsigned PT_SPIN = 1u << 22;
+constexpr float PT_RAISE = 8.f;                   // the running maximum follows a tile's only beyond this (log2 units)
+
+__device__ __forceinline__ float pt_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pt_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
+    const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ qkv, int row_stride,
+    __nv_bfloat16* __restrict__ out, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_qstart,
+    const int* __restrict__ entry_kvlen, int first_entry, int n_entries, int nh, int nkv, float scale_log2, int window, int tpt,
+    int* __restrict__ status) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int G = nh / nkv;
+    const int g = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which entry and which tokens: tiles are taken from the last to the first, the longest blocks start first
+    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, e = first_entry;
+    for (; e < n_entries; ++e) {
+        const int nt = (entry_qstart[e + 1] - entry_qstart[e] + tpt - 1) / tpt;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (e >= n_entries) return;                   // the whole block
+    const int q0 = entry_qstart[e], q1 = entry_qstart[e + 1];
+    const int kvlen = entry_kvlen[e];
+    const int start_pos = kvlen - (q1 - q0);
+    const int tok0 = q0 + tile * tpt;
+    const int n_tok = min(tpt, q1 - tok0);
+    const int rows_valid = n_tok * G;
+    const int* bt = block_table + (size_t)e * bt_stride;
+    const int bpos_first = start_pos + (tok0 - q0), bpos_last = bpos_first + n_tok - 1;
+    const int blo = (window > 0 && bpos_first - window + 1 > 0) ? bpos_first - window + 1 : 0;
+    const int page_first = blo / PT_PAGE, page_last = bpos_last / PT_PAGE;
+    const int n_tiles = (page_last - page_first) / PT_TILE_PAGES + 1;
+
+    unsigned char* q_smem = smem;
+    unsigned char* kv_smem = smem + PT_Q_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_smem + PT_STAGES * PT_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PT_N_BARS);
+    const uint32_t bar0 = t5_smem(bars);
+    const uint32_t q_full = bar0;                                     // Q is in shared memory (128 arrivals)
+    const uint32_t k_full0 = bar0 + 8, v_full0 = k_full0 + 8 * PT_STAGES, kv_empty0 = v_full0 + 8 * PT_STAGES;
+    const uint32_t s_full0 = kv_empty0 + 8 * PT_STAGES;               // a tile's scores are complete (tcgen05.commit)
+    const uint32_t p_full0 = s_full0 + 16;                            // a tile's P is in tensor memory (4 warps)
+    const uint32_t o_done = p_full0 + 16;                             // a tile's P.V has been added to O (tcgen05.commit)
+
+    if (threadIdx.x == 0) {
+        t5_mbar_init(q_full, 128);
+        for (int s = 0; s < PT_STAGES; ++s) {
+            t5_mbar_init(k_full0 + 8 * s, 1);
+            t5_mbar_init(v_full0 + 8 * s, 1);
+            t5_mbar_init(kv_empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            t5_mbar_init(s_full0 + 8 * b, 1);
+            t5_mbar_init(p_full0 + 8 * b, 4);
+        }
+        t5_mbar_init(o_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) t5_alloc(tmem_slot, PT_TMEM_COLS);
+    t5_fence_before();
+    __syncthreads();
+    t5_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- producer: K and V pages of a tile, one box of [16 keys x 64 columns] per lane ----------------
+        constexpr int NBOX = 2 * PT_TILE_PAGES * PT_HALVES;
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int j = 0; j < n_tiles; ++j) {
+            int ok = 1;
+            if (lane == 0) {
+                if (!t5_mbar_wait(kv_empty0 + 8 * stage, phase ^ 1, PT_SPIN)) {
+                    atomicExch(status, 31);
+                    ok = 0;
+                } else {
+                    t5_mbar_expect_tx(k_full0 + 8 * stage, PT_K_BYTES);
+                    t5_mbar_expect_tx(v_full0 + 8 * stage, PT_K_BYTES);
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (lane < NBOX) {
+                const int kv = lane / (PT_TILE_PAGES * PT_HALVES), rem = lane - kv * (PT_TILE_PAGES * PT_HALVES);
+                const int p = rem / PT_HALVES, kk = rem - p * PT_HALVES;
+                const int pidx = min(page_first + j * PT_TILE_PAGES + p, page_last);
+                const int page = bt[pidx];
+                const int row = ((page * 2 + kv) * nkv + g) * PT_PAGE;
+                const uint32_t dst = t5_smem(kv_smem + stage * PT_STAGE_BYTES + kv * PT_K_BYTES + kk * PT_K_HALF + p * (PT_PAGE * 128));
+                t5_tma_2d(dst, &kv_map, kk * 64, row, (kv ? v_full0 : k_full0) + 8 * stage);
+            }
+            if (++stage == PT_STAGES) { stage = 0; phase ^= 1; }
+        }
+    } else if (warp == 1) {
+        // ---------------- tensor-core issue: S(0), S(1), O+=P.V(0), S(2), O+=P.V(1), ... ----------------
+        if (lane == 0) {
+            const uint32_t idesc_s = t5_idesc(PT_ROWS, PT_KEYS, false), idesc_o = t5_idesc(PT_ROWS, PT_HD, true);
+            const uint32_t q_addr = t5_smem(q_smem);
+            bool ok = t5_mbar_wait(q_full, 0, PT_SPIN);
+            if (!ok) atomicExch(status, 32);
+            auto issue_pv = [&](int i) -> bool {
+                const int s = i % PT_STAGES, b = i & 1;
+                if (!t5_mbar_wait(p_full0 + 8 * b, (uint32_t)(i >> 1) & 1u, PT_SPIN)) { atomicExch(status, 33); return false; }
+                if (!t5_mbar_wait(v_full0 + 8 * s, (uint32_t)(i / PT_STAGES) & 1u, PT_SPIN)) { atomicExch(status, 34); return false; }
+                t5_fence_after();
+                const uint32_t v_addr = t5_smem(kv_smem + s * PT_STAGE_BYTES + PT_K_BYTES);
+                const uint32_t p_tmem = tmem_base + (uint32_t)(b * PT_KEYS);
+#pragma unroll
+                for (int kk = 0; kk < PT_KEYS / 16; ++kk)     // 16 keys a product: 8 columns of P, 2 KB of V
+                    t5_mma_ts(tmem_base + PT_COL_O, p_tmem + kk * 8, t5_desc(v_addr + kk * 2048, PT_K_HALF, 1024), idesc_o,
+                              (i > 0 || kk > 0) ? 1u : 0u);
+                t5_commit(kv_empty0 + 8 * s);                 // the stage is free once these products have read it
+                t5_commit(o_done);
+                return true;
+            };
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % PT_STAGES, b = j & 1;
+                if (!t5_mbar_wait(k_full0 + 8 * s, (uint32_t)(j / PT_STAGES) & 1u, PT_SPIN)) { atomicExch(status, 35); ok = false; break; }
+                t5_fence_after();
+                const uint32_t k_addr = t5_smem(kv_smem + s * PT_STAGE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < PT_HD / 16; ++kk) {     // 32 bytes further along head_dim inside the swizzle span
+                    const uint32_t off_q = (kk >> 2) * PT_Q_HALF + (kk & 3) * 32, off_k = (kk >> 2) * PT_K_HALF + (kk & 3) * 32;
+                    t5_mma_ss(tmem_base + (uint32_t)(b * PT_KEYS), t5_desc(q_addr + off_q, 16, 1024), t5_desc(k_addr + off_k, 16, 1024),
+                              idesc_s, kk > 0 ? 1u : 0u);
+                }
+                t5_commit(s_full0 + 8 * b);
+                if (j > 0) ok = issue_pv(j - 1);
+            }
+            if (ok) issue_pv(n_tiles - 1);
+        }
+    } else {
+        // ---------------- softmax and output: warps 2..5 own tensor-memory lanes 32*(warp % 4) .. +31 ----------------
+        const int qd = warp & 3;
+        const int r = qd * 32 + lane;                         // this thread's row
+        const bool rvalid = r < rows_valid;
+        const int tl = rvalid ? r / G : 0, hh = rvalid ? r - tl * G : 0;
+        const int rpos = rvalid ? bpos_first + tl : -1;       // a row that is not there masks every key
+        const int rlo = (rvalid && window > 0 && rpos - window + 1 > 0) ? rpos - window + 1 : 0;
+        {   // Q: this row's head_dim values into the swizzled K-major tile (16-byte chunk c of row r at chunk c ^ (r % 8))
+            const uint4* src = rvalid ? reinterpret_cast<const uint4*>(qkv + (size_t)(tok0 + tl) * row_stride + (size_t)(g * G + hh) * PT_HD) : nullptr;
+#pragma unroll
+            for (int kk = 0; kk < PT_HALVES; ++kk)
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = src ? src[kk * 8 + c] : make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(q_smem + kk * PT_Q_HALF + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+                }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");      // the tensor core reads it through the async proxy
+            t5_mbar_arrive(q_full);
+        }
+        const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int b = j & 1;
+            if (!t5_mbar_wait(s_full0 + 8 * b, (uint32_t)(j >> 1) & 1u, PT_SPIN)) { atomicExch(status, 36); ok = false; break; }
+            t5_fence_after();
+            uint32_t sv[PT_KEYS];
+            t5_ld32(t_lane + b * PT_KEYS, sv);
+            t5_ld32(t_lane + b * PT_KEYS + 32, sv + 32);
+            t5_wait_ld();
+            const int kb = (page_first + j * PT_TILE_PAGES) * PT_PAGE;
+            float mx = -INFINITY;
+            if (kb + PT_KEYS - 1 > rpos || kb < rlo) {        // the tile touches this row's causal or window edge
+#pragma unroll
+                for (int c = 0; c < PT_KEYS; ++c) {
+                    const int key = kb + c;
+                    if (!(key <= rpos && key >= rlo)) sv[c] = __float_as_uint(-INFINITY);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < PT_KEYS; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+            const float mxs = mx * scale_log2;                // scale > 0
+            const bool raise = mxs > m + PT_RAISE;            // also the first keys a row sees (m = -inf)
+            const float m_new = raise ? mxs : m;
+            const float corr = raise ? pt_ex2(m - m_new) : 1.f;   // 0 when nothing was summed yet
+            const float msafe = (m_new == -INFINITY) ? 0.f : m_new;
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < PT_KEYS; c += 2) {
+                const float a = pt_ex2(fmaf(__uint_as_float(sv[c]), scale_log2, -msafe));
+                const float bb = pt_ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -msafe));
+                sum += a + bb;
+                sv[c >> 1] = pt_pack(a, bb);
+            }
+            l = l * corr + sum;
+            m = m_new;
+            if (j > 0) {
+                // O holds the tiles before this one only when their last product is through
+                if (!t5_mbar_wait(o_done, (uint32_t)(j - 1) & 1u, PT_SPIN)) { atomicExch(status, 37); ok = false; break; }
+                t5_fence_after();
+                if (__any_sync(0xffffffffu, raise)) {
+#pragma unroll
+                    for (int c0 = 0; c0 < PT_HD; c0 += 32) {
+                        uint32_t ov[32];
+                        t5_ld32(t_lane + PT_COL_O + c0, ov);
+                        t5_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * corr);
+                        t5_st32(t_lane + PT_COL_O + c0, ov);
+                    }
+                }
+            }
+            t5_st32(t_lane + b * PT_KEYS, sv);                // P over the first half of its own scores
+            t5_wait_st();
+            t5_fence_before();
+            __syncwarp();
+            if (lane == 0) t5_mbar_arrive(p_full0 + 8 * b);
+        }
+        if (ok) {
+            if (!t5_mbar_wait(o_done, (uint32_t)(n_tiles - 1) & 1u, PT_SPIN)) {
+                atomicExch(status, 38);
+            } else {
+                t5_fence_after();
+                const float inv = (l > 0.f) ? 1.f / l : 0.f;
+                __nv_bfloat16* orow = rvalid ? out + (size_t)(tok0 + tl) * nh * PT_HD + (size_t)(g * G + hh) * PT_HD : nullptr;
+#pragma unroll
+                for (int c0 = 0; c0 < PT_HD; c0 += 32) {
+                    uint32_t ov[32];
+                    t5_ld32(t_lane + PT_COL_O + c0, ov);
+                    t5_wait_ld();
+                    if (orow) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 8) {
+                            uint4 v;
+                            v.x = pt_pack(__uint_as_float(ov[c]) * inv, __uint_as_float(ov[c + 1]) * inv);
+                            v.y = pt_pack(__uint_as_float(ov[c + 2]) * inv, __uint_as_float(ov[c + 3]) * inv);
+                            v.z = pt_pack(__uint_as_float(ov[c + 4]) * inv, __uint_as_float(ov[c + 5]) * inv);
+                            v.w = pt_pack(__uint_as_float(ov[c + 6]) * inv, __uint_as_float(ov[c + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c0 + c) = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    t5_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        t5_fence_after();
+        t5_dealloc(tmem_base, PT_TMEM_COLS);
+    }
+}
+
+// Rows a block owns: a tile is 128 / (heads per kv head) tokens.
+IL_EXPORT int il_attn_prefill_tc5_rows() { return PT_ROWS; }
+
+// kv_map: the 128 bytes of the cache's tensor map (boxes of [16 rows x 64 columns], 128-byte swizzle), on the host.
+// n_tiles_total: sum over entries [first_entry, n_entries) of ceil(q_len / tpt), tpt = max(1, 128 / (nh/nkv)).
+IL_EXPORT int il_attn_prefill_tc5(const void* qkv, int row_stride, void* out, const void* kv_map, const int* block_table,
+                                  int bt_stride, const int* entry_qstart, const int* entry_kvlen, int page_size, int first_entry,
+                                  int n_entries, int n_tiles_total, int nh, int nkv, int hd, float scale, int window, int* status,
+                                  cudaStream_t stream) {
+    if (n_tiles_total <= 0 || first_entry >= n_entries) return IL_OK;
+    if (hd != HEAD_DIM || page_size != PT_PAGE || !kv_map || !status) return IL_UNSUPPORTED;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0) return IL_BAD_ARG;
+    const int G = nh / nkv;
+    if (G > PT_ROWS || scale <= 0.f) return IL_UNSUPPORTED;
+    if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || (row_stride & 7)) return IL_UNSUPPORTED;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    static bool attr_set[64];
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        attr_set[dev] = true;
+    }
+    CUtensorMap map;
+    memcpy(&map, kv_map, sizeof(map));
+    dim3 grid(n_tiles_total, nkv);
+    attn_prefill_tc5_kernel<<<grid, PT_THREADS, PT_SMEM, stream>>>(
+        map, (const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, block_table, bt_stride, entry_qstart, entry_kvlen,
+        first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, PT_ROWS / G, status);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}

@@ -14,6 +14,7 @@ from typing import Dict, Mapping, Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager, SequenceCache
 from ..config.model_config import ModelConfig, parse_dtype_name
 from ..config.registry import config_from_json, describe_model, load_config
@@ -90,4 +91,6 @@ class Engine:
         self.runner.use_graphs = True
 
     def synchronize(self) -> None:
+        """Waits for the device and raises if a kernel reported that one of its bounded waits ran out."""
         torch.cuda.current_stream(self.device).synchronize()
+        ops.check_status(self.device)

@@ -324,6 +324,34 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
              int(window or 0), _stream()), "attention_prefill")
 
 
+TC5_PREFILL_ROWS = 128
+
+
+def prefill_tc5_ok(head_dim: int, group: int, page_size: int) -> bool:
+    """Whether the tensor-memory prefill kernel takes this geometry (the caller also needs the cache's tensor map)."""
+    return head_dim in (64, 128) and 0 < group <= TC5_PREFILL_ROWS and page_size == 16
+
+
+def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Tensor, block_table: torch.Tensor,
+                          entry_qstart: torch.Tensor, entry_kvlen: torch.Tensor, first_entry: int, n_entries: int,
+                          n_tiles_total: int, page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
+                          window: Optional[int]) -> None:
+    """The same attention as `attention_prefill`, on tcgen05 tensor cores with tensor memory; `kv_map` is the cache's
+    tensor map (`kv_tensor_map`). n_tiles_total = sum over the entries of ceil(q_len / (128 // (heads/kv_heads)))."""
+    _need_cuda(qkv, out, block_table, entry_qstart, entry_kvlen)
+    if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill_tc5: bfloat16 tensors")
+    if out.shape != (qkv.shape[0], n_heads * head_dim):
+        raise KernelError("attention_prefill_tc5: out [T, heads*head_dim]")
+    _contig("qkv", qkv), _contig("out", out), _contig("block_table", block_table)
+    f = _fn("attn_prefill_tc5", "il_attn_prefill_tc5",
+            [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+             _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+    _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _c_void_p(kv_map.data_ptr()), _ptr(block_table), block_table.shape[1],
+             _ptr(entry_qstart), _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads,
+             head_dim, scale, int(window or 0), _ptr(stream_status(qkv.device)), _stream()), "attention_prefill_tc5")
+
+
 SKINNY_MAX_ROWS = 16
 
 
@@ -359,6 +387,21 @@ def stream_status(device) -> torch.Tensor:
     if key not in _stream_status:
         _stream_status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _stream_status[key]
+
+
+def check_status(device) -> None:
+    """Raises if a kernel with bounded waits (mbarriers of the TMA / tcgen05 kernels) gave up since the last check: its
+    output is then not to be trusted. Reads one word from the device, so it synchronises; call it where the host
+    waits anyway."""
+    key = torch.device(device).index or 0
+    t = _stream_status.get(key)
+    if t is None:
+        return
+    code = int(t.item())
+    if code:
+        t.zero_()
+        raise KernelError(f"a kernel's bounded wait ran out (code {code}: 11-14 gemm_tc5, 21 attn_decode, 31-38 attn_prefill_tc5, "
+                          f"others gemm_stream); the step's results are invalid")
 
 
 def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,

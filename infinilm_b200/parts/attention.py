@@ -9,6 +9,7 @@ ranges of one weight).
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -34,6 +35,7 @@ class Attention(Mixer):
         self.qkv_bias, self.out_bias = bool(p.get("qkv_bias", False)), bool(p.get("out_bias", False))
         self.window: Optional[int] = p.get("window")
         self.force_plain = bool(p.get("plain_kernel", False))
+        self.prefill_kernel = str(p.get("prefill_kernel", os.environ.get("INFINILM_B200_PREFILL_ATTN", "auto")))   # "mma": never tcgen05
         self.scale = 1.0 / math.sqrt(self.hd)
         self.n_qkv = (self.nh + 2 * self.nkv) * self.hd
         self.qkv = Linear(self.hidden, self.n_qkv, dtype)
@@ -107,10 +109,20 @@ class Attention(Mixer):
             # (the kernel can also merge the splits itself, in the last block of each group - `counters=` - but the
             # merge as a second, wide launch measured faster: 3.7 against 3.9 ms for the 8B decode step at batch 8)
         if E > n_dec:
-            tpt = max(1, 64 // G)
+            # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128) and the cache
+            # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.
+            tc5 = (self.prefill_kernel != "mma" and cache.tma_map is not None
+                   and ops.prefill_tc5_ok(self.hd, G, cache.page_size))
+            tpt = max(1, (ops.TC5_PREFILL_ROWS if tc5 else 64) // G)
             n_tiles = sum((q + tpt - 1) // tpt for q in ctx.h_qlen[n_dec:])
-            ops.attention_prefill(qkv, out, cache.storage, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
-                                  n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window)
+            if tc5:
+                ops.attention_prefill_tc5(qkv, out, cache.tma_map, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
+                                          n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
+                                          self.window)
+            else:
+                ops.attention_prefill(qkv, out, cache.storage, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
+                                      n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
+                                      self.window)
 
 
 register_part("mixer", "attention", Attention)

@@ -223,6 +223,52 @@ def test_attention_prefill_bf16(cuda_device, nh, nkv, hd, window):
         close(out.cpu(), c["ref"], "bfloat16")
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 2, 128), (3, 3, 64), (8, 2, 64), (6, 2, 128), (7, 1, 128), (40, 2, 64)])
+@pytest.mark.parametrize("window", [None, 21, 100])
+def test_attention_prefill_tc5(cuda_device, nh, nkv, hd, window):
+    """The tcgen05 / tensor-memory prefill kernel: several entries with offsets, one whole prompt over many key tiles
+    (the running maximum is raised late by the dominating far key), groups that do not divide 128."""
+    G = nh // nkv
+    assert ops.prefill_tc5_ok(hd, G, 16)
+    for starts, qlens in [([0, 47, 16, 3], [33, 2, 17, 2]), ([0], [130]), ([100, 0], [70, 65]), ([5], [420])]:
+        c = _attn_case("bfloat16", nh, nkv, hd, starts, qlens, window, 11, dominate=True)
+        out = torch.full((c["T"], nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+        tpt = max(1, ops.TC5_PREFILL_ROWS // G)
+        n_tiles = sum((q + tpt - 1) // tpt for q in qlens)
+        kv_map = ops.kv_tensor_map(c["cache"])
+        assert kv_map is not None
+        ops.attention_prefill_tc5(c["qkv"], out, kv_map, c["bt"], c["qstart"], c["kvlen"], 0, c["E"], n_tiles, c["page"],
+                                  nh, nkv, hd, 1 / math.sqrt(hd), window)
+        torch.cuda.synchronize()
+        ops.check_status("cuda:0")
+        close(out.cpu(), c["ref"], "bfloat16")
+
+
+def test_attention_prefill_tc5_late_maximum(cuda_device):
+    """Scores that grow along the keys: every tile raises the running maximum by more than the threshold, so the
+    accumulator in tensor memory is rescaled tile after tile; and scores that shrink, where it never is."""
+    nh, nkv, hd, T = 4, 2, 64, 384
+    for sign in (1.0, -1.0):
+        bt, cache = _paged_setup(1, [T], nkv, hd, 16, torch.bfloat16, 3)
+        g = torch.Generator().manual_seed(9)
+        cache.copy_((torch.randn(cache.shape, generator=g) * 0.3).bfloat16())
+        qkv = (torch.randn(T, (nh + 2 * nkv) * hd, generator=g) * 0.3).bfloat16()
+        qkv.view(T, -1, hd)[:, :nh, 0] = 4.0                              # every query looks along dimension 0 ...
+        for t in range(T):                                                # ... where the keys make the score rise (or fall) by 1/8 a key
+            cache[int(bt[0, t // 16]), 0, :, t % 16, 0] = sign * 0.125 * t * math.sqrt(hd) / 4.0
+        tok_pos, tok_entry = torch.arange(T).int(), torch.zeros(T).int()
+        ref = _attn_reference(qkv.float().view(T, -1, hd)[:, :nh], cache.float(), bt, tok_entry, tok_pos, nh, nkv, hd, 16, None)
+        out = torch.full((T, nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+        d_cache = cache.cuda()
+        tpt = ops.TC5_PREFILL_ROWS // (nh // nkv)
+        ops.attention_prefill_tc5(qkv.cuda(), out, ops.kv_tensor_map(d_cache), bt.cuda(), torch.tensor([0, T], dtype=torch.int32).cuda(),
+                                  torch.tensor([T], dtype=torch.int32).cuda(), 0, 1, (T + tpt - 1) // tpt, 16, nh, nkv, hd,
+                                  1 / math.sqrt(hd), None)
+        torch.cuda.synchronize()
+        ops.check_status("cuda:0")
+        close(out.cpu(), ref, "bfloat16")
+
+
 @pytest.mark.parametrize("nh,nkv,hd", SHAPES)
 @pytest.mark.parametrize("window", [None, 40])
 @pytest.mark.parametrize("splits", [1, 3, 7])
