@@ -10,7 +10,7 @@ import plain_model
 from tiny_configs import TINY, make_weights, random_ids, tiny_a, tiny_b
 
 
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_causal_and_deterministic(name):
     raw = TINY[name]()
     w = make_weights(raw, 0)

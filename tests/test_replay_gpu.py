@@ -10,9 +10,9 @@ from tiny_configs import TINY, make_weights, random_ids
 
 pytestmark = pytest.mark.gpu
 
-CASES = [("a", 0), ("b", 1), ("c", 2)]
+CASES = [("a", 0), ("b", 1), ("c", 2), ("d", 3)]
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"a": [5, 17, 33, 100], "b": [3, 40, 70, 100, 200], "c": [2, 31, 64, 129]}
+LENGTHS = {"a": [5, 17, 33, 100], "b": [3, 40, 70, 100, 200], "c": [2, 31, 64, 129], "d": [4, 65, 130, 300]}
 
 
 def _setup(name, seed):

@@ -53,7 +53,26 @@ def tiny_c() -> dict:
     }
 
 
-TINY = {"a": tiny_a, "b": tiny_b, "c": tiny_c}
+def tiny_d() -> dict:
+    # head_dim 64 (the size with TMA / tensor-memory attention kernels), groups of 4, heads*head_dim != hidden,
+    # LongRoPE that stays below its original maximum (short factors), long enough for several key tiles
+    rng = random.Random(11)
+    return {
+        "architectures": ["MiniCPMForCausalLM"], "model_type": "minicpm4",
+        "num_hidden_layers": 2, "hidden_size": 160, "num_attention_heads": 8, "num_key_value_heads": 2,
+        "head_dim": 64, "intermediate_size": 224, "vocab_size": 300,
+        "rope_theta": 20000.0, "max_position_embeddings": 512,
+        "rope_scaling": {"rope_type": "longrope",
+                         "short_factor": [round(rng.uniform(1, 2), 4) for _ in range(32)],
+                         "long_factor": [round(rng.uniform(2, 6), 4) for _ in range(32)],
+                         "original_max_position_embeddings": 512},
+        "scale_emb": 6, "dim_model_base": 80, "scale_depth": 1.2,
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "torch_dtype": "bfloat16",
+        "eos_token_id": 0,
+    }
+
+
+TINY = {"a": tiny_a, "b": tiny_b, "c": tiny_c, "d": tiny_d}
 
 
 def random_ids(n: int, vocab: int, seed: int) -> List[int]:
