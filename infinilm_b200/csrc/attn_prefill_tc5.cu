@@ -14,8 +14,10 @@
 //     O += P.V    tcgen05.mma, M 128, N head_dim, A = P from tensor memory, B = the V pages as they lie in the
 //                 cache (keys by head_dim: MN-major); O accumulates in tensor memory and is divided by the row
 //                 sums at the end.
-//   Roles by warp: 0 producer (TMA, a ring of two K/V stages), 1 tensor-core issue and tensor-memory allocation,
-//   2-5 softmax and output. 256 columns of tensor memory and about 98 KB of shared memory: two blocks per SM.
+//   Roles by warp: 0 producer (TMA; K and V each in a ring of two slots, K freed as soon as its scores are computed,
+//   V when its product is), 1 tensor-core issue and tensor-memory allocation, 2-5 softmax and output. 256 columns of
+//   tensor memory and about 98 KB of shared memory: two blocks per SM, one's products under the other's softmax.
+//   (Two softmax threads a row, each with half the columns, measured slower: 71 against 53 us at 2,048 tokens.)
 //
 //   Pages past the entry's last page are read as the last page again (finite values the mask removes).
 //   Every mbarrier wait is bounded; one that runs out sets *status and all roles leave their loops.
@@ -44,7 +46,7 @@ constexpr int PT_STAGE_BYTES = 2 * PT_K_BYTES;
 constexpr int PT_THREADS = 192;
 constexpr int PT_TMEM_COLS = 256;
 constexpr int PT_COL_O = 2 * PT_KEYS;             // S buffers at columns 0 and 64, O behind them
-constexpr int PT_N_BARS = 1 + 3 * PT_STAGES + 2 + 2 + 1;
+constexpr int PT_N_BARS = 1 + 4 * PT_STAGES + 2 + 2 + 1;
 constexpr int PT_SMEM = 1024 + PT_Q_BYTES + PT_STAGES * PT_STAGE_BYTES + PT_N_BARS * 8 + 16;
 constexpr unsigned PT_SPIN = 1u << 22;
 constexpr float PT_RAISE = 8.f;                   // the running maximum follows a tile's only beyond this (log2 units)
@@ -96,8 +98,8 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PT_N_BARS);
     const uint32_t bar0 = t5_smem(bars);
     const uint32_t q_full = bar0;                                     // Q is in shared memory (128 arrivals)
-    const uint32_t k_full0 = bar0 + 8, v_full0 = k_full0 + 8 * PT_STAGES, kv_empty0 = v_full0 + 8 * PT_STAGES;
-    const uint32_t s_full0 = kv_empty0 + 8 * PT_STAGES;               // a tile's scores are complete (tcgen05.commit)
+    const uint32_t k_full0 = bar0 + 8, v_full0 = k_full0 + 8 * PT_STAGES, k_empty0 = v_full0 + 8 * PT_STAGES;
+    const uint32_t v_empty0 = k_empty0 + 8 * PT_STAGES, s_full0 = v_empty0 + 8 * PT_STAGES;               // a tile's scores are complete (tcgen05.commit)
     const uint32_t p_full0 = s_full0 + 16;                            // a tile's P is in tensor memory (4 warps)
     const uint32_t o_done = p_full0 + 16;                             // a tile's P.V has been added to O (tcgen05.commit)
 
@@ -106,7 +108,8 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
         for (int s = 0; s < PT_STAGES; ++s) {
             t5_mbar_init(k_full0 + 8 * s, 1);
             t5_mbar_init(v_full0 + 8 * s, 1);
-            t5_mbar_init(kv_empty0 + 8 * s, 1);
+            t5_mbar_init(k_empty0 + 8 * s, 1);
+            t5_mbar_init(v_empty0 + 8 * s, 1);
         }
         for (int b = 0; b < 2; ++b) {
             t5_mbar_init(s_full0 + 8 * b, 1);
@@ -123,53 +126,63 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------- producer: K and V pages of a tile, one box of [16 keys x 64 columns] per lane ----------------
-        constexpr int NBOX = 2 * PT_TILE_PAGES * PT_HALVES;
-        int stage = 0;
-        uint32_t phase = 0;
-        for (int j = 0; j < n_tiles; ++j) {
+        // ---------------- producer: K and V pages by TMA, a ring of slots for each ----------------
+        // One K or V tile: lane 0 waits for the ring slot, then one lane per box of [16 keys x 64 columns]. The waits come
+        // in the order in which the tensor core frees the slots: K(j+1) after S(j-1), then V(j) after O+=P.V(j-2).
+        constexpr int NBOX = PT_TILE_PAGES * PT_HALVES;
+        auto issue = [&](int j, int kv) -> bool {
+            const int stage = j % PT_STAGES;
+            const uint32_t full = (kv ? v_full0 : k_full0) + 8 * stage;
             int ok = 1;
             if (lane == 0) {
-                if (!t5_mbar_wait(kv_empty0 + 8 * stage, phase ^ 1, PT_SPIN)) {
+                if (!t5_mbar_wait((kv ? v_empty0 : k_empty0) + 8 * stage, ((uint32_t)(j / PT_STAGES) & 1u) ^ 1u, PT_SPIN)) {
                     atomicExch(status, 31);
                     ok = 0;
                 } else {
-                    t5_mbar_expect_tx(k_full0 + 8 * stage, PT_K_BYTES);
-                    t5_mbar_expect_tx(v_full0 + 8 * stage, PT_K_BYTES);
+                    t5_mbar_expect_tx(full, PT_K_BYTES);
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (lane < NBOX) {
-                const int kv = lane / (PT_TILE_PAGES * PT_HALVES), rem = lane - kv * (PT_TILE_PAGES * PT_HALVES);
-                const int p = rem / PT_HALVES, kk = rem - p * PT_HALVES;
+            if (ok && lane < NBOX) {
+                const int p = lane / PT_HALVES, kk = lane - p * PT_HALVES;
                 const int pidx = min(page_first + j * PT_TILE_PAGES + p, page_last);
                 const int page = bt[pidx];
                 const int row = ((page * 2 + kv) * nkv + g) * PT_PAGE;
                 const uint32_t dst = t5_smem(kv_smem + stage * PT_STAGE_BYTES + kv * PT_K_BYTES + kk * PT_K_HALF + p * (PT_PAGE * 128));
-                t5_tma_2d(dst, &kv_map, kk * 64, row, (kv ? v_full0 : k_full0) + 8 * stage);
+                t5_tma_2d(dst, &kv_map, kk * 64, row, full);
             }
-            if (++stage == PT_STAGES) { stage = 0; phase ^= 1; }
+            return ok != 0;
+        };
+        bool ok = issue(0, 0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            if (j + 1 < n_tiles) ok = issue(j + 1, 0);
+            if (ok) ok = issue(j, 1);
         }
     } else if (warp == 1) {
         // ---------------- tensor-core issue: S(0), S(1), O+=P.V(0), S(2), O+=P.V(1), ... ----------------
         if (lane == 0) {
+            // The issuing thread must keep up with the tensor core (a product every 32 to 64 clocks), so every descriptor
+            // is made here, once: per product only an add of a constant remains. In a descriptor the address field counts
+            // 16-byte units: 32 bytes along K inside the swizzle span are +2, the next 64 columns +half/16.
             const uint32_t idesc_s = t5_idesc(PT_ROWS, PT_KEYS, false), idesc_o = t5_idesc(PT_ROWS, PT_HD, true);
-            const uint32_t q_addr = t5_smem(q_smem);
+            const uint64_t q_desc = t5_desc(t5_smem(q_smem), 16, 1024);
+            const uint64_t k_desc0 = t5_desc(t5_smem(kv_smem), 16, 1024);                  // slot s: + s * slot bytes / 16
+            const uint64_t v_desc0 = t5_desc(t5_smem(kv_smem + PT_K_BYTES), PT_K_HALF, 1024);
+            const uint32_t o_tmem = tmem_base + PT_COL_O;
             bool ok = t5_mbar_wait(q_full, 0, PT_SPIN);
             if (!ok) atomicExch(status, 32);
             auto issue_pv = [&](int i) -> bool {
                 const int s = i % PT_STAGES, b = i & 1;
-                if (!t5_mbar_wait(p_full0 + 8 * b, (uint32_t)(i >> 1) & 1u, PT_SPIN)) { atomicExch(status, 33); return false; }
                 if (!t5_mbar_wait(v_full0 + 8 * s, (uint32_t)(i / PT_STAGES) & 1u, PT_SPIN)) { atomicExch(status, 34); return false; }
+                if (!t5_mbar_wait(p_full0 + 8 * b, (uint32_t)(i >> 1) & 1u, PT_SPIN)) { atomicExch(status, 33); return false; }
                 t5_fence_after();
-                const uint32_t v_addr = t5_smem(kv_smem + s * PT_STAGE_BYTES + PT_K_BYTES);
+                const uint64_t vd = v_desc0 + (uint64_t)(s * (PT_STAGE_BYTES >> 4));
                 const uint32_t p_tmem = tmem_base + (uint32_t)(b * PT_KEYS);
+                t5_mma_ts(o_tmem, p_tmem, vd, idesc_o, i > 0 ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < PT_KEYS / 16; ++kk)     // 16 keys a product: 8 columns of P, 2 KB of V
-                    t5_mma_ts(tmem_base + PT_COL_O, p_tmem + kk * 8, t5_desc(v_addr + kk * 2048, PT_K_HALF, 1024), idesc_o,
-                              (i > 0 || kk > 0) ? 1u : 0u);
-                t5_commit(kv_empty0 + 8 * s);                 // the stage is free once these products have read it
+                for (int kk = 1; kk < PT_KEYS / 16; ++kk)     // 16 keys a product: 8 columns of P, 2 KB of V
+                    t5_mma_ts(o_tmem, p_tmem + kk * 8, vd + (uint64_t)(kk * (2048 >> 4)), idesc_o, 1u);
+                t5_commit(v_empty0 + 8 * s);                  // the V slot is free once these products have read it
                 t5_commit(o_done);
                 return true;
             };
@@ -177,14 +190,16 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
                 const int s = j % PT_STAGES, b = j & 1;
                 if (!t5_mbar_wait(k_full0 + 8 * s, (uint32_t)(j / PT_STAGES) & 1u, PT_SPIN)) { atomicExch(status, 35); ok = false; break; }
                 t5_fence_after();
-                const uint32_t k_addr = t5_smem(kv_smem + s * PT_STAGE_BYTES);
+                const uint64_t kd = k_desc0 + (uint64_t)(s * (PT_STAGE_BYTES >> 4));
+                const uint32_t s_tmem = tmem_base + (uint32_t)(b * PT_KEYS);
 #pragma unroll
-                for (int kk = 0; kk < PT_HD / 16; ++kk) {     // 32 bytes further along head_dim inside the swizzle span
-                    const uint32_t off_q = (kk >> 2) * PT_Q_HALF + (kk & 3) * 32, off_k = (kk >> 2) * PT_K_HALF + (kk & 3) * 32;
-                    t5_mma_ss(tmem_base + (uint32_t)(b * PT_KEYS), t5_desc(q_addr + off_q, 16, 1024), t5_desc(k_addr + off_k, 16, 1024),
-                              idesc_s, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < PT_HD / 16; ++kk) {
+                    const uint64_t off_q = (uint64_t)((kk >> 2) * (PT_Q_HALF >> 4) + (kk & 3) * 2);
+                    const uint64_t off_k = (uint64_t)((kk >> 2) * (PT_K_HALF >> 4) + (kk & 3) * 2);
+                    t5_mma_ss(s_tmem, q_desc + off_q, kd + off_k, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 t5_commit(s_full0 + 8 * b);
+                t5_commit(k_empty0 + 8 * s);                  // and the K slot is free
                 if (j > 0) ok = issue_pv(j - 1);
             }
             if (ok) issue_pv(n_tiles - 1);
@@ -221,7 +236,6 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
             t5_ld32(t_lane + b * PT_KEYS + 32, sv + 32);
             t5_wait_ld();
             const int kb = (page_first + j * PT_TILE_PAGES) * PT_PAGE;
-            float mx = -INFINITY;
             if (kb + PT_KEYS - 1 > rpos || kb < rlo) {        // the tile touches this row's causal or window edge
 #pragma unroll
                 for (int c = 0; c < PT_KEYS; ++c) {
@@ -229,22 +243,25 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
                     if (!(key <= rpos && key >= rlo)) sv[c] = __float_as_uint(-INFINITY);
                 }
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: a single one is all latency
 #pragma unroll
-            for (int c = 0; c < PT_KEYS; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
-            const float mxs = mx * scale_log2;                // scale > 0
+            for (int c = 0; c < PT_KEYS; c += 4)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], __uint_as_float(sv[c + i]));
+            const float mxs = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;      // scale > 0
             const bool raise = mxs > m + PT_RAISE;            // also the first keys a row sees (m = -inf)
             const float m_new = raise ? mxs : m;
             const float corr = raise ? pt_ex2(m - m_new) : 1.f;   // 0 when nothing was summed yet
             const float msafe = (m_new == -INFINITY) ? 0.f : m_new;
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < PT_KEYS; c += 2) {
                 const float a = pt_ex2(fmaf(__uint_as_float(sv[c]), scale_log2, -msafe));
                 const float bb = pt_ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, -msafe));
-                sum += a + bb;
+                sum4[(c >> 1) & 3] += a + bb;
                 sv[c >> 1] = pt_pack(a, bb);
             }
-            l = l * corr + sum;
+            l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             m = m_new;
             if (j > 0) {
                 // O holds the tiles before this one only when their last product is through
