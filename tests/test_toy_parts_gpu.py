@@ -1,8 +1,10 @@
 """A toy architecture defined here, in the test, built and stepped without a change to the
-framework's files: a mixer with state of its own (a decaying sum kept in a state slot), layers
-that differ from one another, a run order that names a layer twice and lets one entry read
-another entry's cache. It is compared with a plain whole-sequence computation under several ways
-of cutting the work. The toy parts use torch for their arithmetic; they are test code, not a model."""
+framework's files: a mixer with state of its own (a decaying sum kept in a state slot), a
+feed-forward that routes every token to one of several experts, a position encoding of its own
+(rotation angles that grow with the square root of the pair index, damped), layers that differ
+from one another, a run order that names a layer twice and lets one entry read another entry's
+cache. It is compared with a plain whole-sequence computation under several ways of cutting the
+work. The toy parts use torch for their arithmetic; they are test code, not a model."""
 import math
 from dataclasses import dataclass
 
@@ -17,8 +19,8 @@ pytestmark = pytest.mark.gpu
 
 from infinilm_b200.config import ModelConfig, config_from_json, register_architecture, unregister_architecture  # noqa: E402
 from infinilm_b200.engine import Engine  # noqa: E402
-from infinilm_b200.parts import (CacheNeed, LayerSpec, Mixer, ModelSpec, PartSpec, RunStep, WeightSpec,  # noqa: E402
-                                 register_part, unregister_part)
+from infinilm_b200.parts import (CacheNeed, FeedForward, LayerSpec, Mixer, ModelSpec, PartSpec, PositionEncoding, RunStep,  # noqa: E402
+                                 WeightSpec, register_part, unregister_part)
 from infinilm_b200.weights import random_tensors  # noqa: E402
 
 
@@ -54,6 +56,56 @@ class DecayMixer(Mixer):
         return out.to(x.dtype)
 
 
+def sqrt_inv_freq(rot_dim: int, base: float):
+    return [base / math.sqrt(i + 1.0) for i in range(rot_dim // 2)]
+
+
+class SqrtPosition(PositionEncoding):
+    """A rotary encoding with its own table: angle = position * base / sqrt(i + 1), cos/sin times `damp`.
+    The attention mixer applies whatever table the position part it was given exposes."""
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        self.rot_dim, self.mscale = int(params["rot_dim"]), float(params["damp"])
+        self._table = sqrt_inv_freq(self.rot_dim, float(params["base"]))
+
+    def to_device(self, device):
+        self.inv_freq = torch.tensor(self._table, dtype=torch.float64).to(torch.float32).to(device)
+
+
+class Top1Experts(FeedForward):
+    """Every token goes to the expert with the largest router logit (f32), a SwiGLU of its own; the output is the
+    expert's, times the logit's sigmoid. A function of the token's row alone, so any cutting gives the same."""
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        self.h, self.inter, self.n = int(params["hidden"]), int(params["intermediate"]), int(params["experts"])
+
+    def weight_specs(self):
+        specs = [WeightSpec("router.weight", (self.n, self.h), init=("normal", 0.3))]
+        for e in range(self.n):
+            specs += [WeightSpec(f"experts.{e}.gate.weight", (self.inter, self.h), init=("normal", 0.05)),
+                      WeightSpec(f"experts.{e}.up.weight", (self.inter, self.h), init=("normal", 0.05)),
+                      WeightSpec(f"experts.{e}.down.weight", (self.h, self.inter), init=("normal", 0.05))]
+        return specs
+
+    def set_weights(self, t):
+        self.w = {k: v.float() for k, v in t.items()}
+
+    def forward(self, x, ctx):
+        xf = x.float()
+        logits = xf @ self.w["router.weight"].t()
+        top, which = logits.max(dim=1)
+        out = torch.zeros_like(xf)
+        for e in range(self.n):
+            rows = (which == e).nonzero().flatten()
+            if rows.numel():
+                xe = xf[rows]
+                y = torch.nn.functional.silu(xe @ self.w[f"experts.{e}.gate.weight"].t()) * (xe @ self.w[f"experts.{e}.up.weight"].t())
+                out[rows] = (y @ self.w[f"experts.{e}.down.weight"].t()) * torch.sigmoid(top[rows])[:, None]
+        return out.to(x.dtype)
+
+
 @dataclass
 class ToyConfig(ModelConfig):
     n_heads: int = 0
@@ -73,6 +125,7 @@ class ToyConfig(ModelConfig):
 
 ORDER = [RunStep(0), RunStep(1), RunStep(0), RunStep(1, cache_from=1)]
 BRANCH = 0.6
+N_EXPERTS, POS_BASE, POS_DAMP = 3, 0.7, 0.9
 
 
 def describe_toy(cfg: ToyConfig) -> ModelSpec:
@@ -80,9 +133,9 @@ def describe_toy(cfg: ToyConfig) -> ModelSpec:
 
     def norm(p):
         return PartSpec("rmsnorm", {"size": H, "eps": cfg.eps}, p)
-    rope = PartSpec("rope", {"rot_dim": cfg.head_dim, "theta": 10000.0})
+    rope = PartSpec("toy_sqrt", {"rot_dim": cfg.head_dim - 4, "base": POS_BASE, "damp": POS_DAMP})
     l0 = LayerSpec("prenorm_residual", norm("toy.l0.n1"), PartSpec("toy_decay", {"hidden": H, "decay": cfg.decay}, "toy.l0.mixer"),
-                   norm("toy.l0.n2"), PartSpec("swiglu", {"hidden": H, "intermediate": cfg.inter}, "toy.l0.mlp"),
+                   norm("toy.l0.n2"), PartSpec("toy_top1", {"hidden": H, "intermediate": cfg.inter, "experts": N_EXPERTS}, "toy.l0.moe"),
                    {"residual_scale": BRANCH})
     l1 = LayerSpec("prenorm_residual", norm("toy.l1.n1"),
                    PartSpec("attention", {"hidden": H, "n_heads": cfg.n_heads, "n_kv_heads": cfg.n_kv_heads,
@@ -102,14 +155,33 @@ RAW = {"architectures": ["ToyForCausalLM"], "model_type": "toy", "vocab_size": 2
 @pytest.fixture()
 def toy():
     register_part("mixer", "toy_decay", DecayMixer)
+    register_part("feed_forward", "toy_top1", Top1Experts)
+    register_part("position", "toy_sqrt", SqrtPosition)
     register_architecture(["ToyForCausalLM", "toy"], ToyConfig, describe_toy)
     yield
     unregister_architecture("ToyForCausalLM")
     unregister_part("mixer", "toy_decay")
+    unregister_part("feed_forward", "toy_top1")
+    unregister_part("position", "toy_sqrt")
 
 
-def plain_toy(w, ids, round_bf16):
-    """The toy model on whole sequences, from plain_model's parts and the recurrence above."""
+def plain_top1(w, p, x, margins):
+    """The routed feed-forward on whole sequences; appends each token's routing margin (top logit minus the
+    second, over the top's size) to `margins`."""
+    logits = x @ w[f"{p}.router.weight"].float().t()
+    srt = logits.sort(dim=1, descending=True).values
+    margins += ((srt[:, 0] - srt[:, 1]) / srt[:, 0].abs().clamp_min(1e-6)).tolist()
+    out = torch.zeros_like(x)
+    for t in range(x.shape[0]):
+        e = int(logits[t].argmax())
+        y = torch.nn.functional.silu(x[t] @ w[f"{p}.experts.{e}.gate.weight"].float().t()) * (x[t] @ w[f"{p}.experts.{e}.up.weight"].float().t())
+        out[t] = (y @ w[f"{p}.experts.{e}.down.weight"].float().t()) * torch.sigmoid(logits[t, e])
+    return out
+
+
+def plain_toy(w, ids, round_bf16, margins=None):
+    """The toy model on whole sequences, from plain_model's parts and the recurrences above."""
+    margins = [] if margins is None else margins
     cfg = {"num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 16, "hidden_size": 96, "rope_theta": 10000.0,
            "max_position_embeddings": 256}
     T = len(ids)
@@ -132,44 +204,72 @@ def plain_toy(w, ids, round_bf16):
             q = plain_model.linear(x, w[f"{a}.q_proj.weight"]).view(T, 6, 16)
             k = plain_model.linear(x, w[f"{a}.k_proj.weight"]).view(T, 2, 16)
             v = plain_model.linear(x, w[f"{a}.v_proj.weight"]).view(T, 2, 16)
-            cos, sin = plain_model.rope_tables(cfg, pos)
-            q, k = plain_model.apply_rope(q, cos, sin, 16), plain_model.apply_rope(k, cos, sin, 16)
+            ang = pos.float()[:, None] * torch.tensor(sqrt_inv_freq(12, POS_BASE), dtype=torch.float64).float()[None, :]
+            cos, sin = torch.cos(ang) * POS_DAMP, torch.sin(ang) * POS_DAMP
+            q, k = plain_model.apply_rope(q, cos, sin, 12), plain_model.apply_rope(k, cos, sin, 12)
             if st.cache_from is None:
                 kv_of[i] = (k, v)
             else:
                 k, v = kv_of[st.cache_from]
             branch = plain_model.linear(plain_model.attention_scores(q, k, v), w[f"{a}.o_proj.weight"])
         h = h + BRANCH * branch
-        h = h + BRANCH * plain_model.swiglu_mlp(w, f"{p}.mlp", plain_model.rms_norm(h, w[f"{p}.n2.weight"], 1e-5))
+        x2 = plain_model.rms_norm(h, w[f"{p}.n2.weight"], 1e-5)
+        h = h + BRANCH * (plain_top1(w, f"{p}.moe", x2, margins) if st.layer == 0 else plain_model.swiglu_mlp(w, f"{p}.mlp", x2))
     h = plain_model.rms_norm(h, w["toy.norm.weight"], 1e-5)
     return plain_model.linear(h, w["toy.embed.weight"], None, 0.5)
 
 
+# A token whose two best router logits are nearly equal may go to another expert when the arithmetic changes (bfloat16
+# against the plain float32 computation): that is a property of routing, not a fault. So each case names the smallest
+# routing margin it relies on, the test checks it on the plain computation, and the bfloat16 case uses a weight seed
+# and lengths for which every margin is wide (found by search on the CPU).
+SCENARIOS = {
+    "float32": dict(seed=4, n=90, cuts=([90], [58] + [1] * 32, [16, 7, 2, 5, 3, 17, 2, 1, 31, 6]), margin=1e-4,
+                    lens={"a": 40, "b": 70, "c": 33, "d": 60},
+                    sched=[[("a", 16), ("b", 30)], [("a", 1), ("b", 1), ("c", 33)], [("a", 23), ("b", 39)], [("d", 2)], [("d", 57)], [("d", 1)]]),
+    "bfloat16": dict(seed=73, n=40, cuts=([40], [24] + [1] * 16, [7, 2, 5, 3, 17, 2, 1, 3]), margin=0.05,
+                     lens={"a": 12, "b": 20, "c": 9},
+                     sched=[[("a", 5), ("b", 9)], [("a", 1), ("b", 1), ("c", 9)], [("a", 6), ("b", 10)]]),
+}
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_toy_architecture_builds_and_steps(cuda_device, toy, dtype):
+    sc = SCENARIOS[dtype]
     cfg = config_from_json(RAW)
     assert isinstance(cfg, ToyConfig)
-    w = random_tensors(cfg, 4, "cpu", tie=True)
-    assert "toy.l0.mixer.mix.weight" in w and "toy.head.weight" not in w
+    w = random_tensors(cfg, sc["seed"], "cpu", tie=True)
+    assert "toy.l0.mixer.mix.weight" in w and "toy.l0.moe.experts.2.down.weight" in w and "toy.head.weight" not in w
     eng = Engine.from_tensors(cfg, w, dtype=dtype, page_size=16, num_pages=24, max_seqs=4, max_batch_tokens=256)
     # two state caches (layer 0 runs twice) in one group, one paged cache (entry 3 reads entry 1's)
     kinds = [(g.need.kind, g.entries) for g in eng.cache.groups]
     assert kinds == [("state", [0, 2]), ("paged_kv", [1])]
     tol = {"float32": 2e-5, "bfloat16": 2.5e-2}[dtype]
-    ids = random_ids(90, 211, 1)
-    ref = plain_toy(w, ids, dtype == "bfloat16")
-    for cuts in ([90], [58] + [1] * 32, [16, 7, 2, 5, 3, 17, 2, 1, 31, 6]):
-        got = run_cut(eng, ids, cuts)
+    margins = []
+    ids = random_ids(sc["n"], 211, 1)
+    ref = plain_toy(w, ids, dtype == "bfloat16", margins)
+    for cuts in sc["cuts"]:
+        got = run_cut(eng, ids, list(cuts))
         bad = first_bad_row(got, ref, tol)
         assert bad is None, f"cuts {cuts[:4]}..: first wrong position {bad}, rel err {rel_err(got, ref):.3e}"
     # mixed requests: state slots and pages of finished requests are used again
-    reqs = {k: random_ids(n, 211, 10 + i) for i, (k, n) in enumerate({"a": 40, "b": 70, "c": 33, "d": 60}.items())}
-    sched = [[("a", 16), ("b", 30)], [("a", 1), ("b", 1), ("c", 33)], [("a", 23), ("b", 39)], [("d", 2)], [("d", 57)], [("d", 1)]]
-    got = run_schedule(eng, reqs, sched)
-    for k, r in reqs.items():
-        bad = first_bad_row(got[k], plain_toy(w, r, dtype == "bfloat16"), tol)
+    reqs = {k: random_ids(n, 211, 10 + i) for i, (k, n) in enumerate(sc["lens"].items())}
+    refs = {k: plain_toy(w, r, dtype == "bfloat16", margins) for k, r in reqs.items()}
+    assert min(margins) >= sc["margin"], f"this case needs routing margins of {sc['margin']}, the plain computation has {min(margins):.2e}"
+    got = run_schedule(eng, reqs, sc["sched"])
+    for k in reqs:
+        bad = first_bad_row(got[k], refs[k], tol)
         assert bad is None, f"request {k}: first wrong position {bad}"
     assert not eng.cache.live and eng.cache.slots.n_free == 4
+
+
+def test_toy_experts_all_used(toy):
+    """The routed feed-forward of the cases above really routes: every expert gets tokens."""
+    cfg = config_from_json(RAW)
+    w = random_tensors(cfg, 4, "cpu", tie=True)
+    x = plain_model.rms_norm(plain_model.embed(torch.tensor(random_ids(90, 211, 1)), w["toy.embed.weight"], 2.0, False), w["toy.l0.n2.weight"], 1e-5)
+    which = (x @ w["toy.l0.moe.router.weight"].float().t()).argmax(dim=1)
+    assert sorted(set(which.tolist())) == list(range(N_EXPERTS))
 
 
 def test_unknown_part_kind_is_named(cuda_device):
