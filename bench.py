@@ -219,6 +219,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
+                    help="tokens cached per request before decoding (a multiple of 2,048; default: the configuration's 2,048). "
+                         "With more, prompts go in portions of 2,048 and `prefill` times the LAST portion, over the cache of the others")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
     ap.add_argument("--points", type=str, default="1,64", help="batch sizes of the extra decode points")
@@ -264,8 +267,12 @@ def main() -> int:
     dev = "cuda:0"
     torch.cuda.set_device(0)
     K, W = args.steps, args.warmup
+    P = args.prompt_len
+    if P % PROMPT_LEN or P <= 0 or P + 2 * (K + W) + 8 > cfg.max_position_embeddings:
+        print(f"--prompt-len must be a positive multiple of {PROMPT_LEN} that leaves room for the decoded tokens")
+        return 2
     max_b = max([args.batch] + ([] if args.no_points else [int(b) for b in args.points.split(',') if b]))
-    pages_per_req = (PROMPT_LEN + 2 * (K + W) + 8 + PAGE - 1) // PAGE + 1
+    pages_per_req = (P + 2 * (K + W) + (args.batch * P + 4095) // 4096 + args.batch + 16 + PAGE - 1) // PAGE + 1
     num_pages = max_b * pages_per_req + 8
 
     t_setup = time.time()
@@ -276,25 +283,30 @@ def main() -> int:
     del tensors
     eng = llm.engine
     g = torch.Generator().manual_seed(1)
-    prompts = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in range(max_b)]
+    prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=g).tolist() for _ in range(max_b)]
     wbytes, _ = weight_bytes(cfg, n_layers)
     kv_per_token = eng.cache.bytes_per_token(2)
 
-    def flops_prefill(T):
+    def flops_prefill(T, before=0):
         _, per_layer = weight_bytes(cfg, n_layers)
         lin = 2.0 * T * (per_layer - 2 * cfg.hidden_size) * n_layers + 2.0 * cfg.vocab_size * cfg.hidden_size
-        attn = 4.0 * (T * (T + 1) / 2) * cfg.num_attention_heads * cfg.head_dim * n_layers
+        attn = 4.0 * (T * before + T * (T + 1) / 2) * cfg.num_attention_heads * cfg.head_dim * n_layers
         return lin + attn
 
-    # ---- prefill: one 2,048-token prompt, one step --------------------------------------------
+    def feed(seq, ids, upto):                     # a prompt's tokens [0, upto) in portions of 2,048, nothing wanted
+        for a in range(0, upto, PROMPT_LEN):
+            eng.step([StepEntry(seq, ids[a:a + PROMPT_LEN], [])])
+
+    # ---- prefill: one portion of 2,048 tokens, one step (the whole prompt at the default length) ------
     def time_prefill(reps):
         times = []
         for i in range(reps):
             seq = eng.open(("pf", i))
+            feed(seq, prompts[0], P - PROMPT_LEN)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             e0.record()
-            eng.step([StepEntry(seq, prompts[0], [PROMPT_LEN - 1])])
+            eng.step([StepEntry(seq, prompts[0][P - PROMPT_LEN:], [PROMPT_LEN - 1])])
             e1.record()
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1))
@@ -303,13 +315,15 @@ def main() -> int:
     time_prefill(2)
     pf_ms = statistics.median(time_prefill(3))
     prefill = {"value": PROMPT_LEN / (pf_ms / 1e3), "tokens": PROMPT_LEN, "ms": pf_ms,
-               "frac": flops_prefill(PROMPT_LEN) / (pf_ms / 1e3) / (tf_peak * 1e12)}
+               "frac": flops_prefill(PROMPT_LEN, P - PROMPT_LEN) / (pf_ms / 1e3) / (tf_peak * 1e12)}
+    if P != PROMPT_LEN:
+        prefill["cached_before"] = P - PROMPT_LEN
 
     # ---- decode on the device: B requests with 2,048 tokens cached, K timed steps -----------------
     def time_decode(B, clocks=None):
         seqs = [eng.open(("d", B, i)) for i in range(B)]
         for i, s in enumerate(seqs):
-            eng.step([StepEntry(s, prompts[i], [])])
+            feed(s, prompts[i], P)
         toks = [[(7 * i + 3) % cfg.vocab_size] for i in range(B)]
 
         def one():
@@ -347,7 +361,9 @@ def main() -> int:
             points[f"decode_b{B}"] = B / (ms_b / 1e3)
 
     # ---- end to end through the Python entry point ------------------------------------------------
-    sp = SamplingParams(top_k=1, max_tokens=K + W + 2, ignore_eos=True)
+    # no request may reach its limit inside the timed steps: those that finish their prompt first decode while the others' prompts go in
+    n_prompt_steps = (args.batch * P + 4095) // 4096 + args.batch
+    sp = SamplingParams(top_k=1, max_tokens=K + W + n_prompt_steps + 4, ignore_eos=True)
     reqs = [llm.add_request(prompts[i], sp) for i in range(args.batch)]
     while any(len(r.output_token_ids) < 1 for r in reqs):
         llm.step()
@@ -374,7 +390,7 @@ def main() -> int:
         "config": {"model": "MiniCPM4-8B sizes", "layers": n_layers, "layers_of_config": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "global_batch": args.batch, "prompt_len": PROMPT_LEN, "context": CONTEXT,
+                   "global_batch": args.batch, "prompt_len": P, "context": max(CONTEXT, P + 2 * (K + W) + 8),
                    "seq_len": int(ctx_end), "page_size": PAGE, "parallelism": "single GPU",
                    "cuda_graph": not args.no_graph, "l2": "inputs larger than L2 (weights 16 GB per step)",
                    "peaks": peak_src},
