@@ -28,7 +28,7 @@ constexpr int AD_PAGE = 16;                       // keys per tile = page size t
 constexpr int AD_STAGES = 2;                      // 4 warps x 2 stages of a page (8-9 KB at head_dim 128): three blocks fit on an SM
 constexpr int AD_STAGE_BYTES = 2 * AD_PAGE * AT_ROW_BYTES;
 constexpr int AD_SMEM_PIPE = AD_WARPS * AD_STAGES * AD_STAGE_BYTES;
-constexpr int AD_SMEM_MERGE = AD_WARPS * 16 * (HEAD_DIM + 2) * 4;
+constexpr int AD_SMEM_MERGE = AD_WARPS * 16 * (HEAD_DIM + 4 + 2) * 4;   // the warps' scaled outputs and their (m, l)
 constexpr int AD_SMEM = (AD_SMEM_PIPE > AD_SMEM_MERGE ? AD_SMEM_PIPE : AD_SMEM_MERGE) + AD_WARPS * AD_STAGES * 8 + 1024;
 constexpr bool AD_TMA_OK = (HEAD_DIM % 64 == 0);
 constexpr int AD_BOXES = HEAD_DIM / 64;           // 64-column boxes of a K (or V) block
@@ -55,34 +55,50 @@ __device__ __forceinline__ uint32_t ad_swz(uint32_t block, int r, int ch) {
 
 constexpr int AD_MAX_SPLITS = 128;
 
-// One warp merges the splits of one (token, head) row: the split factors exp2(m_s - M) are computed once (lanes over
-// splits) and kept in `fs` (shared memory, AD_MAX_SPLITS floats of this warp); then each lane sums four output columns.
-__device__ __forceinline__ void ad_merge_row(float* fs, const float* __restrict__ o_part, const float* __restrict__ ml_part,
+// One warp merges the splits of one (token, head) row. Every load is issued before anything waits for one: the
+// (maximum, sum) pairs of all splits in one pass (lanes over splits), then the partial outputs sixteen splits at a
+// time, each lane four columns. The split factors exp2(m_s - M) go through `fs` (shared memory, AD_MAX_SPLITS floats
+// of this warp). A chain of dependent loads, one split after the other, is what this merge would otherwise cost.
+__device__ __forceinline__ void ad_merge_row(float* fs, const float* o_part, const float* ml_part,
                                              size_t row, int n_valid, int n_splits, __nv_bfloat16* __restrict__ out, int lane) {
     const size_t pr0 = row * n_splits;
+    constexpr int PER_LANE = AD_MAX_SPLITS / 32;
+    float2 ml[PER_LANE];
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int s = lane + 32 * i;
+        ml[i] = s < n_valid ? *reinterpret_cast<const float2*>(ml_part + (pr0 + s) * 2) : make_float2(-INFINITY, 0.f);
+    }
     float M = -INFINITY;
-    for (int s = lane; s < n_valid; s += 32) M = fmaxf(M, ml_part[(pr0 + s) * 2]);
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) M = fmaxf(M, ml[i].x);
     M = il_warp_max(M);
     float L = 0.f;
-    for (int s = lane; s < n_valid; s += 32) {
-        const float ms = ml_part[(pr0 + s) * 2];
-        const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-        fs[s] = f;
-        L += f * ml_part[(pr0 + s) * 2 + 1];
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int s = lane + 32 * i;
+        const float f = (ml[i].x == -INFINITY) ? 0.f : exp2f(ml[i].x - M);
+        if (s < n_valid) fs[s] = f;
+        L += f * ml[i].y;
     }
     L = il_warp_sum(L);
     __syncwarp();
     const float inv = 1.f / L;
     for (int d = lane * 4; d < AT_HD; d += 128) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-        for (int s = 0; s < n_valid; ++s) {
-            const float4 v = *reinterpret_cast<const float4*>(o_part + (pr0 + s) * AT_HD + d);
-            const float f = fs[s];
-            acc.x += f * v.x;
-            acc.y += f * v.y;
-            acc.z += f * v.z;
-            acc.w += f * v.w;
+        for (int s0 = 0; s0 < n_valid; s0 += 16) {
+            float4 v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                v[i] = s0 + i < n_valid ? *reinterpret_cast<const float4*>(o_part + (pr0 + s0 + i) * AT_HD + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {        // in split order: the same sum whatever the chunking
+                const float f = s0 + i < n_valid ? fs[s0 + i] : 0.f;
+                acc.x += f * v[i].x;
+                acc.y += f * v[i].y;
+                acc.z += f * v[i].z;
+                acc.w += f * v[i].w;
+            }
         }
         const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
         *reinterpret_cast<uint2*>(out + row * AT_HD + d) = make_uint2(a, b);
@@ -90,15 +106,19 @@ __device__ __forceinline__ void ad_merge_row(float* fs, const float* __restrict_
     __syncwarp();
 }
 
+// (qkv, and o_part / ml_part in the merge, are written by the kernel before and read after a wait that is not the
+// kernel's first statement: they are not declared __restrict__, so that no load of them is treated as read-only
+// data and scheduled above the wait.)
 __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
-    const __nv_bfloat16* __restrict__ qkv, int row_stride, const __nv_bfloat16* __restrict__ cache,
+    const __nv_bfloat16* qkv, int row_stride, const __nv_bfloat16* __restrict__ cache,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
     float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, int use_tma, int* __restrict__ status,
     int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    il_pdl_begin();
+    // Lengths, block tables and the pages of earlier tokens do not come from the kernel before this one (it writes q and
+    // the newest token's slot in the last page): what depends only on them is done before waiting for that kernel.
     const int split = blockIdx.x;
     const int G = nh / nkv;
     const int row_tiles = (G + 15) / 16;
@@ -121,10 +141,6 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int head0 = g * G + rt * 16;            // first query head of this row tile
     const int rows_valid = min(16, G - rt * 16);
 
-    uint32_t qf[AT_KSTEPS][4];
-    const __nv_bfloat16* qbase = qkv + (size_t)e * row_stride;
-    at_load_q(qf, [&](int r) { return r < rows_valid ? qbase + (size_t)(head0 + r) * AT_HD : nullptr; }, lane);
-
     float o[AT_NT][4];
 #pragma unroll
     for (int i = 0; i < AT_NT; ++i)
@@ -144,6 +160,42 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
         }
         return __shfl_sync(0xffffffffu, my_ids, it - ids_base);
     };
+    // the tensor-copy pipeline of this warp; its first page is asked for now if it is not the last page of the request
+    const bool tma = AD_TMA_OK && use_tma;
+    const uint32_t tpipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_TMA_STAGE_BYTES;
+    const uint32_t tbars = (uint32_t)__cvta_generic_to_shared(smem) + AD_WARPS * AD_STAGES * AD_TMA_STAGE_BYTES + warp * AD_STAGES * 8;
+    auto tma_issue = [&](int it) {
+        if (it < n_my) {
+            const int page = page_of(it);
+            if (lane == 0) {
+                const uint32_t st = tpipe + (it % AD_STAGES) * AD_TMA_STAGE_BYTES, bar = tbars + (it % AD_STAGES) * 8;
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the tile was read by ldmatrix before
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(AD_TMA_STAGE_BYTES) : "memory");
+                const int rk = ((page * 2) * nkv + g) * AD_PAGE, rv = ((page * 2 + 1) * nkv + g) * AD_PAGE;
+#pragma unroll
+                for (int bx = 0; bx < AD_BOXES; ++bx) {
+                    ad_tma_2d(st + bx * 2048, &kv_map, bx * 64, rk, bar);
+                    ad_tma_2d(st + (AD_BOXES + bx) * 2048, &kv_map, bx * 64, rv, bar);
+                }
+            }
+        }
+    };
+    int n_early = 0;                              // iterations whose copies are already under way
+    if (tma) {
+        if (lane == 0) {
+            for (int st = 0; st < AD_STAGES; ++st) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(tbars + st * 8));
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        }
+        __syncwarp();
+        for (; n_early < AD_STAGES && p0 + warp + n_early * AD_WARPS < last_page; ++n_early) tma_issue(n_early);
+    }
+    il_pdl_begin();
+
+    uint32_t qf[AT_KSTEPS][4];
+    const __nv_bfloat16* qbase = qkv + (size_t)e * row_stride;
+    at_load_q(qf, [&](int r) { return r < rows_valid ? qbase + (size_t)(head0 + r) * AT_HD : nullptr; }, lane);
+
     // One page: scores, online softmax, P.V. `qk` fills s[2][4] from the K tile, `pv` adds P.V from the V tile.
     auto softmax_page = [&](float (&s)[2][4], int it, uint32_t (&pf)[4]) {
         const int key0 = (p0 + warp + it * AD_WARPS) * AD_PAGE + (lane & 3) * 2;
@@ -181,36 +233,12 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
         }
     };
 
-    if (AD_TMA_OK && use_tma) {
+    if (tma) {
         // ---- tensor copies into swizzled tiles, one mbarrier per warp and stage ----
-        const uint32_t pipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_TMA_STAGE_BYTES;
-        const uint32_t bars = (uint32_t)__cvta_generic_to_shared(smem) + AD_WARPS * AD_STAGES * AD_TMA_STAGE_BYTES + warp * AD_STAGES * 8;
-        if (lane == 0) {
-            for (int st = 0; st < AD_STAGES; ++st) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bars + st * 8));
-            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        }
-        __syncwarp();
-        auto issue = [&](int it) {
-            if (it < n_my) {
-                const int page = page_of(it);
-                if (lane == 0) {
-                    const uint32_t st = pipe + (it % AD_STAGES) * AD_TMA_STAGE_BYTES, bar = bars + (it % AD_STAGES) * 8;
-                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the tile was read by ldmatrix before
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(AD_TMA_STAGE_BYTES) : "memory");
-                    const int rk = ((page * 2) * nkv + g) * AD_PAGE, rv = ((page * 2 + 1) * nkv + g) * AD_PAGE;
-#pragma unroll
-                    for (int bx = 0; bx < AD_BOXES; ++bx) {
-                        ad_tma_2d(st + bx * 2048, &kv_map, bx * 64, rk, bar);
-                        ad_tma_2d(st + (AD_BOXES + bx) * 2048, &kv_map, bx * 64, rv, bar);
-                    }
-                }
-            }
-        };
-#pragma unroll
-        for (int s = 0; s < AD_STAGES - 1; ++s) issue(s);
+        const uint32_t pipe = tpipe, bars = tbars;
+        auto issue = tma_issue;
+        for (int s = n_early; s < AD_STAGES; ++s) issue(s);
         for (int it = 0; it < n_my; ++it) {
-            issue(it + AD_STAGES - 1);
             if (!ad_mbar_wait(bars + (it % AD_STAGES) * 8, (it / AD_STAGES) & 1)) {
                 if (lane == 0) atomicExch(status, 21);
                 break;
@@ -244,6 +272,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
                 }
             }
             __syncwarp();
+            issue(it + AD_STAGES);                // refill the stage this page came from
         }
     } else {
         // ---- per-lane asynchronous copies into padded tiles ----
@@ -274,41 +303,57 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     }
     __syncthreads();                              // the pipeline memory is reused for the merge
 
-    // merge the four warps: each writes (m, l, O) for its 16 rows
-    float* mo = reinterpret_cast<float*>(smem) + (size_t)warp * 16 * (AT_HD + 2);
+    // Merge the four warps. Each puts its rows' (m, l) into shared memory; then every thread knows its rows' common
+    // maximum M, scales its part of O by 2^(m - M) in registers and writes it out; then the four parts are added, in
+    // warp order, sixteen bytes at a time. (One exponential per row and warp: computing them per output element cost
+    // this kernel more than its pages did.)
+    float* sm_ml = reinterpret_cast<float*>(smem);                     // [warp][16 rows][m, l]
+    float* sm_o = sm_ml + AD_WARPS * 16 * 2;                           // [warp][16 rows][AT_HD + 4]
+    constexpr int OS = AT_HD + 4;
+    if ((lane & 3) == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = (lane >> 2) + 8 * h;
+            sm_ml[(warp * 16 + r) * 2] = m[h];
+            sm_ml[(warp * 16 + r) * 2 + 1] = l[h];
+        }
+    }
+    __syncthreads();
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = (lane >> 2) + 8 * h;
-        float* row = mo + (size_t)r * (AT_HD + 2);
-        if ((lane & 3) == 0) {
-            row[AT_HD] = m[h];
-            row[AT_HD + 1] = l[h];
-        }
+        float M = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < AT_NT; ++nt) {
-            row[nt * 8 + (lane & 3) * 2] = o[nt][2 * h];
-            row[nt * 8 + (lane & 3) * 2 + 1] = o[nt][2 * h + 1];
-        }
+        for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+        const float f = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - M);
+        float* row = sm_o + (size_t)(warp * 16 + r) * OS + (lane & 3) * 2;
+#pragma unroll
+        for (int nt = 0; nt < AT_NT; ++nt) *reinterpret_cast<float2*>(row + nt * 8) = make_float2(f * o[nt][2 * h], f * o[nt][2 * h + 1]);
     }
     il_pdl_tail();
     __syncthreads();
-    const float* all = reinterpret_cast<const float*>(smem);
-    for (int idx = threadIdx.x; idx < rows_valid * AT_HD; idx += AD_WARPS * 32) {
-        const int r = idx / AT_HD, d = idx - r * AT_HD;
-        float M = -INFINITY;
+    for (int idx = threadIdx.x; idx < rows_valid * (AT_HD / 4); idx += AD_WARPS * 32) {
+        const int r = idx / (AT_HD / 4), d = (idx - r * (AT_HD / 4)) * 4;
+        float4 acc = *reinterpret_cast<const float4*>(sm_o + (size_t)r * OS + d);
 #pragma unroll
-        for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, all[((size_t)w * 16 + r) * (AT_HD + 2) + AT_HD]);
-        float acc = 0.f, L = 0.f;
-#pragma unroll
-        for (int w = 0; w < AD_WARPS; ++w) {
-            const float* row = all + ((size_t)w * 16 + r) * (AT_HD + 2);
-            const float f = (row[AT_HD] == -INFINITY) ? 0.f : exp2f(row[AT_HD] - M);
-            acc += f * row[d];
-            L += f * row[AT_HD + 1];
+        for (int w = 1; w < AD_WARPS; ++w) {
+            const float4 v = *reinterpret_cast<const float4*>(sm_o + (size_t)(w * 16 + r) * OS + d);
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
         }
         const size_t pr = ((size_t)e * nh + head0 + r) * n_splits + split;
-        o_part[pr * AT_HD + d] = acc;
+        *reinterpret_cast<float4*>(o_part + pr * AT_HD + d) = acc;
         if (d == 0) {
+            float M = -INFINITY, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+#pragma unroll
+            for (int w = 0; w < AD_WARPS; ++w) {
+                const float mw = sm_ml[(w * 16 + r) * 2];
+                L += ((mw == -INFINITY) ? 0.f : exp2f(mw - M)) * sm_ml[(w * 16 + r) * 2 + 1];
+            }
             ml_part[pr * 2] = M;
             ml_part[pr * 2 + 1] = L;
         }
@@ -338,21 +383,21 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
 
 // The merge as a kernel of its own (one warp per (token, head)), for callers that do not give the attention kernel
 // a counter array to find its last block with.
-__global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
+__global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_part, const float* ml_part,
                                                                 const int* __restrict__ entry_kvlen, int nh, int n_rows, int window,
                                                                 int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out) {
     __shared__ float fs[4][AD_MAX_SPLITS];
-    il_pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + warp;        // = e * nh + head
-    if (row >= n_rows) return;
-    const int e = row / nh;
-    const int kvlen = entry_kvlen[e];
+    // the lengths come with the step's descriptors, not from the kernel before: read them while that one still runs
+    const int kvlen = row < n_rows ? entry_kvlen[row / nh] : 1;
     const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
     const int n_pages = (kvlen - 1) / AD_PAGE - lo / AD_PAGE + 1;
     if (pages_per_split <= 0) pages_per_split = (n_pages + n_splits - 1) / n_splits;
     int n_valid = (n_pages + pages_per_split - 1) / pages_per_split;
     if (n_valid > n_splits) n_valid = n_splits;
+    il_pdl_wait();
+    if (row >= n_rows) return;
     ad_merge_row(fs[warp], o_part, ml_part, (size_t)row, n_valid, n_splits, out, lane);
 }
 

@@ -72,7 +72,10 @@ __device__ __forceinline__ float il_block_max(float v, float* sh) {
 // while this one drains (INFINILM_B200_PDL=0 turns it off). A kernel waits for its predecessor to have
 // finished and flushed (il_pdl_begin) before it touches anything another kernel produces or reads, and
 // lets its successor in once its main loop is over (il_pdl_tail; a kernel without one does so by ending).
-// Both are no-ops in a kernel that was launched the ordinary way. Measured on the 8B decode step at
+// Both are no-ops in a kernel that was launched the ordinary way. A kernel may do, before its wait, whatever does not
+// depend on its predecessor (read weights, step descriptors, cache pages of earlier tokens). What the predecessor
+// writes must then NOT be read through a `const __restrict__` pointer: such loads count as read-only data for the
+// whole kernel (ld.global.nc) and were seen scheduled above the wait, which replayed graphs then showed as wrong tokens. Measured on the 8B decode step at
 // batch 8: 3.65 ms so, 3.70 ms without; with every kernel letting its successor in at its very start
 // (IL_PDL_MODE 0) 6.7 ms, because waiting blocks of later kernels then crowd the SMs.
 __device__ __forceinline__ void il_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }

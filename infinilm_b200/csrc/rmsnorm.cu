@@ -49,16 +49,23 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
 }
 
 template <typename TA, int MAXV>
-__global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restrict__ branch, float bscale,
+__global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* resid, const TA* branch, float bscale,
                                                               const void* __restrict__ w, int w_kind, float eps, TA* __restrict__ out,
                                                               const int* __restrict__ rows, int H) {
     __shared__ float red[32];
-    il_pdl_begin();
     const int i = blockIdx.x;
+    const int nv = H >> 2;                        // float4 groups in a row
+    // the norm's weights and the row index do not come from the kernel before this one: read while it still runs
+    float4 wv[MAXV];
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+        const int v = threadIdx.x + k * 256;
+        wv[k] = v < nv ? (w_kind == IL_F32 ? ld4((const float*)w + 4 * v) : ld4((const __nv_bfloat16*)w + 4 * v)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     const int r = rows ? rows[i] : i;
+    il_pdl_wait();
     float* rr = resid + (size_t)r * H;
     const TA* br = branch ? branch + (size_t)r * H : nullptr;
-    const int nv = H >> 2;                        // float4 groups in a row
     float4 x[MAXV];
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
@@ -96,10 +103,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict_
 #pragma unroll
     for (int k = 0; k < MAXV; ++k) {
         const int v = threadIdx.x + k * 256;
-        if (v < nv) {
-            const float4 wv = w_kind == IL_F32 ? ld4((const float*)w + 4 * v) : ld4((const __nv_bfloat16*)w + 4 * v);
-            st4(o + 4 * v, make_float4(x[k].x * rstd * wv.x, x[k].y * rstd * wv.y, x[k].z * rstd * wv.z, x[k].w * rstd * wv.w));
-        }
+        if (v < nv) st4(o + 4 * v, make_float4(x[k].x * rstd * wv[k].x, x[k].y * rstd * wv[k].y, x[k].z * rstd * wv[k].z, x[k].w * rstd * wv[k].w));
     }
 }
 

@@ -17,20 +17,35 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const in
                                   const int* __restrict__ tok_entry, const int* __restrict__ block_table,
                                   int bt_stride, TA* __restrict__ cache, int page_size, int nh, int nkv, int hd,
                                   int rot, const float* __restrict__ inv_freq, float mscale) {
-    il_pdl_begin();
+    // Positions, block tables and the angle table do not come from the kernel before this one: all of that is done
+    // before waiting for it. After the wait a thread reads its pairs once and writes them where they go: q and k back
+    // into the row, k and v into the cache slot.
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     TA* row = qkv + (size_t)t * row_stride;
     const int half = rot >> 1;
     __shared__ float cs[128], sn[128];            // rot <= head_dim <= 256
-    if (half > 0) {
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            float s, c;
-            sincosf((float)pos * inv_freq[i], &s, &c);
-            sn[i] = s * mscale;
-            cs[i] = c * mscale;
+    TA* kdst = nullptr;                           // this token's K slot of kv head 0, or null: nothing to store
+    size_t head_step = 0, v_off = 0;
+    if (cache) {
+        const int e = tok_entry[t];
+        const int page = block_table[(size_t)e * bt_stride + pos / page_size];
+        if (page >= 0) {                          // the host reserves every page a step touches; never write elsewhere
+            head_step = (size_t)page_size * hd;
+            v_off = (size_t)nkv * head_step;
+            kdst = cache + (size_t)page * 2 * v_off + (size_t)(pos % page_size) * hd;
         }
-        __syncthreads();
+    }
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        sn[i] = s * mscale;
+        cs[i] = c * mscale;
+    }
+    __syncthreads();
+    il_pdl_launch_dependents();                   // the attention kernel behind this one has a prologue of its own to run meanwhile
+    il_pdl_wait();
+    if (half > 0) {
         if ((half & 1) == 0) {                    // two neighbouring pairs per thread, 4- or 8-byte accesses
             const int hp = half >> 1, n2 = (nh + nkv) * hp;
             for (int idx = threadIdx.x; idx < n2; idx += blockDim.x) {
@@ -38,8 +53,15 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const in
                 TA* base = row + (size_t)j * hd;
                 const float2 a = ld2(base + i), b = ld2(base + i + half);
                 const float s0 = sn[i], c0 = cs[i], s1 = sn[i + 1], c1 = cs[i + 1];
-                st2(base + i, make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1));
-                st2(base + i + half, make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1));
+                const float2 lo = make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+                const float2 hi = make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+                st2(base + i, lo);
+                st2(base + i + half, hi);
+                if (j >= nh && kdst) {
+                    TA* kd = kdst + (size_t)(j - nh) * head_step;
+                    st2(kd + i, lo);
+                    st2(kd + i + half, hi);
+                }
             }
         } else {
             const int n_pairs = (nh + nkv) * half;
@@ -48,29 +70,32 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const in
                 TA* base = row + (size_t)j * hd;
                 const float s = sn[i], c = cs[i];
                 const float x1 = il_to_f(base[i]), x2 = il_to_f(base[i + half]);
-                base[i] = il_from_f<TA>(x1 * c - x2 * s);
-                base[i + half] = il_from_f<TA>(x2 * c + x1 * s);
+                const TA lo = il_from_f<TA>(x1 * c - x2 * s), hi = il_from_f<TA>(x2 * c + x1 * s);
+                base[i] = lo;
+                base[i + half] = hi;
+                if (j >= nh && kdst) {
+                    TA* kd = kdst + (size_t)(j - nh) * head_step;
+                    kd[i] = lo;
+                    kd[i + half] = hi;
+                }
             }
         }
     }
-    if (!cache) return;
-    __syncthreads();
-    const int e = tok_entry[t];
-    const int page = block_table[(size_t)e * bt_stride + pos / page_size];
-    if (page < 0) return;  // the host reserves every page a step touches; never write elsewhere
-    const int off = pos % page_size;
+    if (!kdst) return;
+    // what the rotation did not touch: k beyond rot (nothing when rot == head_dim), and v
     const TA* ksrc = row + (size_t)nh * hd;
     const TA* vsrc = ksrc + (size_t)nkv * hd;
-    const size_t page_elems = (size_t)2 * nkv * page_size * hd;
-    TA* kdst = cache + (size_t)page * page_elems;
-    TA* vdst = kdst + (size_t)nkv * page_size * hd;
+    const int tail = hd - rot;
+    for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
+        const int g = idx / tail, c = rot + (idx - g * tail);
+        kdst[(size_t)g * head_step + c] = ksrc[(size_t)g * hd + c];
+    }
     constexpr int VEC = 16 / sizeof(TA);          // elements per 16-byte chunk; head_dim is a multiple of 16
     const int cpr = hd / VEC;
     for (int idx = threadIdx.x; idx < nkv * cpr; idx += blockDim.x) {
         const int g = idx / cpr, c = idx - g * cpr;
-        const size_t o = ((size_t)g * page_size + off) * hd + (size_t)c * VEC;
-        *reinterpret_cast<uint4*>(kdst + o) = *reinterpret_cast<const uint4*>(ksrc + (size_t)g * hd + (size_t)c * VEC);
-        *reinterpret_cast<uint4*>(vdst + o) = *reinterpret_cast<const uint4*>(vsrc + (size_t)g * hd + (size_t)c * VEC);
+        *reinterpret_cast<uint4*>(kdst + v_off + (size_t)g * head_step + (size_t)c * VEC) =
+            *reinterpret_cast<const uint4*>(vsrc + (size_t)g * hd + (size_t)c * VEC);
     }
 }
 
