@@ -45,57 +45,86 @@ __global__ void rope_store_kernel(TA* __restrict__ qkv, int row_stride, const in
     __syncthreads();
     il_pdl_launch_dependents();                   // the attention kernel behind this one has a prologue of its own to run meanwhile
     il_pdl_wait();
-    if (half > 0) {
-        if ((half & 1) == 0) {                    // two neighbouring pairs per thread, 4- or 8-byte accesses
-            const int hp = half >> 1, n2 = (nh + nkv) * hp;
-            for (int idx = threadIdx.x; idx < n2; idx += blockDim.x) {
-                const int j = idx / hp, i = (idx - j * hp) * 2;
-                TA* base = row + (size_t)j * hd;
-                const float2 a = ld2(base + i), b = ld2(base + i + half);
-                const float s0 = sn[i], c0 = cs[i], s1 = sn[i + 1], c1 = cs[i + 1];
-                const float2 lo = make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
-                const float2 hi = make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
-                st2(base + i, lo);
-                st2(base + i + half, hi);
-                if (j >= nh && kdst) {
-                    TA* kd = kdst + (size_t)(j - nh) * head_step;
-                    st2(kd + i, lo);
-                    st2(kd + i + half, hi);
+    // After the wait every load of a batch is issued before its first store: the row is read and written in place, so
+    // the compiler keeps loads behind earlier stores, and a loop of load-rotate-store rounds would pay the memory
+    // latency once per round.
+    constexpr int VEC = 16 / sizeof(TA);          // elements per 16-byte chunk; head_dim is a multiple of 16
+    const int cpr = hd / VEC;
+    const TA* ksrc = row + (size_t)nh * hd;
+    const TA* vsrc = ksrc + (size_t)nkv * hd;
+    constexpr int UV = 2, UR = 4;
+    for (int vb = 0; vb < (kdst ? nkv * cpr : 0) || vb == 0; vb += UV * blockDim.x) {
+        uint4 vv[UV];
+        const int n_v = kdst ? nkv * cpr : 0;
+#pragma unroll
+        for (int u = 0; u < UV; ++u) {
+            const int idx = vb + u * blockDim.x + threadIdx.x;
+            if (idx < n_v) vv[u] = *reinterpret_cast<const uint4*>(vsrc + (size_t)(idx / cpr) * hd + (size_t)(idx % cpr) * VEC);
+        }
+        if (vb == 0 && half > 0) {
+            if ((half & 1) == 0) {                // two neighbouring pairs per thread, 4- or 8-byte accesses
+                const int hp = half >> 1, n2 = (nh + nkv) * hp;
+                for (int rb = 0; rb < n2; rb += UR * blockDim.x) {
+                    float2 a[UR], b[UR];
+#pragma unroll
+                    for (int u = 0; u < UR; ++u) {
+                        const int idx = rb + u * blockDim.x + threadIdx.x;
+                        if (idx < n2) {
+                            const int j = idx / hp, i = (idx - j * hp) * 2;
+                            a[u] = ld2(row + (size_t)j * hd + i);
+                            b[u] = ld2(row + (size_t)j * hd + i + half);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < UR; ++u) {
+                        const int idx = rb + u * blockDim.x + threadIdx.x;
+                        if (idx < n2) {
+                            const int j = idx / hp, i = (idx - j * hp) * 2;
+                            TA* base = row + (size_t)j * hd;
+                            const float s0 = sn[i], c0 = cs[i], s1 = sn[i + 1], c1 = cs[i + 1];
+                            const float2 lo = make_float2(a[u].x * c0 - b[u].x * s0, a[u].y * c1 - b[u].y * s1);
+                            const float2 hi = make_float2(b[u].x * c0 + a[u].x * s0, b[u].y * c1 + a[u].y * s1);
+                            st2(base + i, lo);
+                            st2(base + i + half, hi);
+                            if (j >= nh && kdst) {
+                                TA* kd = kdst + (size_t)(j - nh) * head_step;
+                                st2(kd + i, lo);
+                                st2(kd + i + half, hi);
+                            }
+                        }
+                    }
                 }
-            }
-        } else {
-            const int n_pairs = (nh + nkv) * half;
-            for (int idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
-                const int j = idx / half, i = idx - j * half;
-                TA* base = row + (size_t)j * hd;
-                const float s = sn[i], c = cs[i];
-                const float x1 = il_to_f(base[i]), x2 = il_to_f(base[i + half]);
-                const TA lo = il_from_f<TA>(x1 * c - x2 * s), hi = il_from_f<TA>(x2 * c + x1 * s);
-                base[i] = lo;
-                base[i + half] = hi;
-                if (j >= nh && kdst) {
-                    TA* kd = kdst + (size_t)(j - nh) * head_step;
-                    kd[i] = lo;
-                    kd[i + half] = hi;
+            } else {
+                const int n_pairs = (nh + nkv) * half;
+                for (int idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+                    const int j = idx / half, i = idx - j * half;
+                    TA* base = row + (size_t)j * hd;
+                    const float s = sn[i], c = cs[i];
+                    const float x1 = il_to_f(base[i]), x2 = il_to_f(base[i + half]);
+                    const TA lo = il_from_f<TA>(x1 * c - x2 * s), hi = il_from_f<TA>(x2 * c + x1 * s);
+                    base[i] = lo;
+                    base[i + half] = hi;
+                    if (j >= nh && kdst) {
+                        TA* kd = kdst + (size_t)(j - nh) * head_step;
+                        kd[i] = lo;
+                        kd[i + half] = hi;
+                    }
                 }
             }
         }
+#pragma unroll
+        for (int u = 0; u < UV; ++u) {
+            const int idx = vb + u * blockDim.x + threadIdx.x;
+            if (idx < n_v)
+                *reinterpret_cast<uint4*>(kdst + v_off + (size_t)(idx / cpr) * head_step + (size_t)(idx % cpr) * VEC) = vv[u];
+        }
     }
     if (!kdst) return;
-    // what the rotation did not touch: k beyond rot (nothing when rot == head_dim), and v
-    const TA* ksrc = row + (size_t)nh * hd;
-    const TA* vsrc = ksrc + (size_t)nkv * hd;
+    // what the rotation did not touch of k: the dimensions beyond rot (none when rot == head_dim)
     const int tail = hd - rot;
     for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
         const int g = idx / tail, c = rot + (idx - g * tail);
         kdst[(size_t)g * head_step + c] = ksrc[(size_t)g * hd + c];
-    }
-    constexpr int VEC = 16 / sizeof(TA);          // elements per 16-byte chunk; head_dim is a multiple of 16
-    const int cpr = hd / VEC;
-    for (int idx = threadIdx.x; idx < nkv * cpr; idx += blockDim.x) {
-        const int g = idx / cpr, c = idx - g * cpr;
-        *reinterpret_cast<uint4*>(kdst + v_off + (size_t)g * head_step + (size_t)c * VEC) =
-            *reinterpret_cast<const uint4*>(vsrc + (size_t)g * hd + (size_t)c * VEC);
     }
 }
 
@@ -106,7 +135,10 @@ IL_EXPORT int il_rope_store(void* qkv, int act_kind, int row_stride, const int* 
     if (hd > 256) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || hd <= 0 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0) return IL_BAD_ARG;
     if (row_stride < (nh + 2 * nkv) * hd || hd % 16 != 0 || row_stride % 8 != 0) return IL_BAD_ARG;
-    const int threads = 256;
+    // a thread takes up to four pairs of neighbours at once: enough threads that one round covers a row
+    const int pairs2 = (nh + nkv) * (rot / 4);
+    int threads = ((pairs2 + 3) / 4 + 31) / 32 * 32;
+    threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
     if (act_kind == IL_F32)
         IL_LAUNCH(rope_store_kernel<float>, T, threads, 0, stream, (float*)qkv, row_stride, tok_pos, tok_entry, block_table, bt_stride,
                                                             (float*)cache, page_size, nh, nkv, hd, rot, inv_freq, mscale);
