@@ -31,7 +31,7 @@ template <> __device__ __forceinline__ void gs_store<__nv_bfloat16>(__nv_bfloat1
 
 // NT: 8-row groups of x (1: M <= 8, 2: M <= 16). GLU: 0 plain, 1 SwiGLU (W holds N gate rows, then N up rows). U: blocks in flight.
 template <int NT, int GLU, int U, typename TO>
-__global__ void __launch_bounds__(GS_WARPS * 32) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+__global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
                                                                     const __nv_bfloat16* __restrict__ W, int ldw, TO* __restrict__ out,
                                                                     int ldo, const float* __restrict__ bias, float alpha, int M, int N, int K) {
     constexpr int NW = 1;
@@ -145,6 +145,159 @@ IL_EXPORT int il_gemm_skinny(const void* x, int ldx, const void* W, int ldw, voi
         else if (out_kind == IL_BF16) e = gs_launch<2, 0, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
         else e = gs_launch<2, 0, float>(x, ldx, W, ldw, out, ldo, bias, alpha, M, N, K, stream);
     }
+    if (e != cudaSuccess) return 1000 + (int)e;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- the q/k/v projection of a decode step with the rotary encoding and the cache write in its epilogue -------------
+// out[M, (nh + 2 nkv) hd] = x . W^T (+ bias) as above, then q and k heads rotated (rotate-half pairs (d, d + rot/2),
+// angle pos * inv_freq[d], cos and sin times mscale) and k, v written to their token's slot of the paged cache: what
+// rope_store does as a kernel of its own. A block's 16 rows of W are, for the rotated part of a head, 8 rows at
+// d0.. and the 8 rows at d0 + rot/2.. they pair with (the SwiGLU tiling in another guise); elsewhere 16 rows in a row.
+// The product is rounded to bfloat16 before it is rotated, as it is when the two kernels run one after the other, so a
+// token's keys do not depend on which path it took. rot and head_dim - rot must be multiples of 16.
+struct GsRope {
+    const int* tok_pos;
+    const int* tok_entry;
+    const int* block_table;
+    int bt_stride;
+    __nv_bfloat16* cache;                         // [page][2][nkv][page_size][hd], or null: nothing is stored
+    int page_size, nh, nkv, hd, rot;
+    const float* inv_freq;
+    float mscale;
+};
+
+template <int NT, int U>
+__global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_rope_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                                                                         const __nv_bfloat16* __restrict__ W, int ldw,
+                                                                         __nv_bfloat16* __restrict__ out, int ldo,
+                                                                         const float* __restrict__ bias, float alpha, int M, int K,
+                                                                         const GsRope rp) {
+    __shared__ float part[GS_WARPS][NT][16][8];
+    __shared__ float cs[NT * 8][8], sn[NT * 8][8];
+    __shared__ long long slot[NT * 8];            // element offset of the token's K slot of kv head 0 in the cache, or -1
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, c = lane & 3;
+    const int tiles_per_head = rp.hd >> 4, half = rp.rot >> 1;
+    const int j = blockIdx.x / tiles_per_head, tl = blockIdx.x - j * tiles_per_head;    // head (q, then k, then v) and tile in it
+    const bool rotated = j < rp.nh + rp.nkv && tl < (rp.rot >> 4);
+    const int d0 = rotated ? tl * 8 : (j < rp.nh + rp.nkv ? rp.rot + (tl - (rp.rot >> 4)) * 16 : tl * 16);
+    const int step = rotated ? half : 8;          // distance between the two rows a lane reads, = between a tile's two halves
+    const int n_lo = j * rp.hd + d0;              // output column of the tile's row 0; row 8 + i is column n_lo + step + i
+    const __nv_bfloat16* wrow[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) wrow[h] = W + (size_t)(n_lo + r + h * step) * ldw;
+    // positions, slots and angles come with the step's descriptors: made ready while the kernel before still runs
+    for (int i = threadIdx.x; i < NT * 8 * 8; i += GS_WARPS * 32) {
+        const int m = i >> 3, nl = i & 7;
+        float sv = 0.f, cv = 1.f;
+        if (rotated && m < M) {
+            sincosf((float)rp.tok_pos[m] * rp.inv_freq[d0 + nl], &sv, &cv);
+            sv *= rp.mscale;
+            cv *= rp.mscale;
+        }
+        sn[m][nl] = sv;
+        cs[m][nl] = cv;
+    }
+    if (threadIdx.x < NT * 8) {
+        const int m = threadIdx.x;
+        long long off = -1;
+        if (m < M && rp.cache && j >= rp.nh) {
+            const int pos = rp.tok_pos[m];
+            const int page = rp.block_table[(size_t)rp.tok_entry[m] * rp.bt_stride + pos / rp.page_size];
+            if (page >= 0) off = ((long long)page * 2 * rp.nkv * rp.page_size + pos % rp.page_size) * rp.hd;
+        }
+        slot[m] = off;
+    }
+    il_pdl_begin();
+    const __nv_bfloat16* xrow[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) xrow[t] = (t * 8 + r < M) ? x + (size_t)(t * 8 + r) * ldx : nullptr;
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[t][q] = 0.f;
+    const int nkb = (K + 31) >> 5;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int kb0 = warp; kb0 < nkb; kb0 += GS_WARPS * U) {
+        uint4 a[U][2], b[U][NT];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (kb0 + u * GS_WARPS) * 32 + c * 8;
+            const bool ok = k < K;
+            a[u][0] = ok ? gs_ld_stream(wrow[0] + k) : zero;
+            a[u][1] = ok ? gs_ld_stream(wrow[1] + k) : zero;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) b[u][t] = (ok && xrow[t]) ? gs_ld(xrow[t] + k) : zero;
+        }
+        __syncwarp();                             // keeps every load above issued before the first product waits for one
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                gs_mma(acc[t], a[u][0].x, a[u][1].x, a[u][0].y, a[u][1].y, b[u][t].x, b[u][t].y);
+                gs_mma(acc[t], a[u][0].z, a[u][1].z, a[u][0].w, a[u][1].w, b[u][t].z, b[u][t].w);
+            }
+    }
+    il_pdl_tail();
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        part[warp][t][r][c * 2] = acc[t][0];
+        part[warp][t][r][c * 2 + 1] = acc[t][1];
+        part[warp][t][r + 8][c * 2] = acc[t][2];
+        part[warp][t][r + 8][c * 2 + 1] = acc[t][3];
+    }
+    __syncthreads();
+    const bool to_cache = j >= rp.nh;
+    const int kv = j >= rp.nh + rp.nkv ? 1 : 0, g = j - rp.nh - kv * rp.nkv;            // for k and v heads
+    const size_t head_off = ((size_t)kv * rp.nkv + (to_cache ? g : 0)) * rp.page_size * rp.hd;
+    for (int idx = threadIdx.x; idx < NT * 8 * 8; idx += GS_WARPS * 32) {
+        const int nl = idx & 7, m = idx >> 3;     // consecutive threads: consecutive output columns
+        if (m >= M) continue;
+        const int t = m >> 3, mc = m & 7;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < GS_WARPS; ++w) {
+            s0 += part[w][t][nl][mc];
+            s1 += part[w][t][nl + 8][mc];
+        }
+        const int n1 = n_lo + nl, n2 = n1 + step;
+        // rounded as the product alone would store them, then rotated
+        const float y1 = __bfloat162float(__float2bfloat16_rn(alpha * s0 + (bias ? bias[n1] : 0.f)));
+        const float y2 = __bfloat162float(__float2bfloat16_rn(alpha * s1 + (bias ? bias[n2] : 0.f)));
+        const float cv = cs[m][nl], sv = sn[m][nl];
+        const __nv_bfloat16 lo = __float2bfloat16_rn(rotated ? y1 * cv - y2 * sv : y1);
+        const __nv_bfloat16 hi = __float2bfloat16_rn(rotated ? y2 * cv + y1 * sv : y2);
+        out[(size_t)m * ldo + n1] = lo;
+        out[(size_t)m * ldo + n2] = hi;
+        if (to_cache && slot[m] >= 0) {
+            __nv_bfloat16* dst = rp.cache + (size_t)slot[m] + head_off + (d0 + nl);
+            dst[0] = lo;
+            dst[step] = hi;
+        }
+    }
+}
+
+// The fused form for 1..16 rows; the shapes it takes: rot and head_dim - rot multiples of 16 (rot may be 0).
+IL_EXPORT int il_gemm_skinny_rope(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, const float* bias, float alpha,
+                                  int M, int K, const int* tok_pos, const int* tok_entry, const int* block_table, int bt_stride,
+                                  void* cache, int page_size, int nh, int nkv, int hd, int rot, const float* inv_freq, float mscale,
+                                  cudaStream_t stream) {
+    if (M <= 0) return IL_OK;
+    const int N = (nh + 2 * nkv) * hd;
+    if (M > 16 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K || ldo < N) return IL_UNSUPPORTED;
+    if (nh <= 0 || nkv <= 0 || hd <= 0 || (hd & 15) || rot < 0 || rot > hd || (rot & 15) || page_size <= 0) return IL_UNSUPPORTED;
+    if (rot > 0 && !inv_freq) return IL_BAD_ARG;
+    GsRope rp{tok_pos, tok_entry, block_table, bt_stride, (__nv_bfloat16*)cache, page_size, nh, nkv, hd, rot, inv_freq, mscale};
+    cudaError_t e;
+    if (M <= 8)
+        e = il_launch(gemm_skinny_rope_kernel<1, 8>, dim3(N / 16), dim3(GS_WARPS * 32), 0, stream, (const __nv_bfloat16*)x, ldx,
+                      (const __nv_bfloat16*)W, ldw, (__nv_bfloat16*)out, ldo, bias, alpha, M, K, rp);
+    else
+        e = il_launch(gemm_skinny_rope_kernel<2, 4>, dim3(N / 16), dim3(GS_WARPS * 32), 0, stream, (const __nv_bfloat16*)x, ldx,
+                      (const __nv_bfloat16*)W, ldw, (__nv_bfloat16*)out, ldo, bias, alpha, M, K, rp);
     if (e != cudaSuccess) return 1000 + (int)e;
     IL_LAUNCH_CHECK();
     return IL_OK;

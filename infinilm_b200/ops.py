@@ -374,6 +374,43 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: floa
              M, N, K, int(glu), _stream()), "gemm_skinny")
 
 
+def skinny_rope_ok(M: int, K: int, head_dim: int, rot_dim: int) -> bool:
+    """Whether `gemm_skinny_rope` takes this shape: a few rows, rotary and head sizes in steps of 16."""
+    return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and head_dim % 16 == 0 and rot_dim % 16 == 0 and 0 <= rot_dim <= head_dim
+
+
+def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float, bias: Optional[torch.Tensor],
+                     tok_pos: torch.Tensor, tok_entry: torch.Tensor, block_table: torch.Tensor, cache: Optional[torch.Tensor],
+                     page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, rot_dim: int,
+                     inv_freq: Optional[torch.Tensor], mscale: float) -> None:
+    """The q/k/v projection of up to 16 bfloat16 rows with what `rope_store` does in its epilogue: out[M, (heads + 2
+    kv_heads) * head_dim] = alpha * x @ w^T (+ bias), q and k rotated, k and v written to their cache slots (if `cache`)."""
+    _need_cuda(x, w, out, bias, tok_pos, tok_entry, block_table, cache, inv_freq)
+    M, K = x.shape
+    N = (n_heads + 2 * n_kv_heads) * head_dim
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or tuple(w.shape) != (N, K) or out.shape != (M, N):
+        raise KernelError(f"gemm_skinny_rope: bfloat16 x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_skinny_rope: innermost dimension must be contiguous")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_skinny_rope: bias float32, one per weight row")
+    if tok_pos.dtype != torch.int32 or tok_entry.dtype != torch.int32 or block_table.dtype != torch.int32 or tok_pos.numel() < M:
+        raise KernelError("gemm_skinny_rope: descriptors must be int32, one position and entry per row")
+    if rot_dim > 0 and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2):
+        raise KernelError("gemm_skinny_rope: inv_freq float32 [rot_dim/2]")
+    _contig("block_table", block_table)
+    if cache is not None:
+        _contig("cache", cache)
+        if cache.dtype != torch.bfloat16 or tuple(cache.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+            raise KernelError("gemm_skinny_rope: cache bfloat16 [pages,2,kv_heads,page,head_dim]")
+    f = _fn("gemm_skinny", "il_gemm_skinny_rope",
+            [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p,
+             _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _ptr(bias), alpha, M, K, _ptr(tok_pos),
+             _ptr(tok_entry), _ptr(block_table), block_table.shape[1], _ptr(cache), page_size, n_heads, n_kv_heads, head_dim,
+             rot_dim, _ptr(inv_freq), mscale, _stream()), "gemm_skinny_rope")
+
+
 def skinny_ok(M: int, K: int) -> bool:
     return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0
 

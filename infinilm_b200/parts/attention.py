@@ -36,6 +36,7 @@ class Attention(Mixer):
         self.window: Optional[int] = p.get("window")
         self.force_plain = bool(p.get("plain_kernel", False))
         self.prefill_kernel = str(p.get("prefill_kernel", os.environ.get("INFINILM_B200_PREFILL_ATTN", "auto")))   # "mma": never tcgen05
+        self.fuse_rope = os.environ.get("INFINILM_B200_FUSE_ROPE", "1") != "0"
         self.scale = 1.0 / math.sqrt(self.hd)
         self.n_qkv = (self.nh + 2 * self.nkv) * self.hd
         self.qkv = Linear(self.hidden, self.n_qkv, dtype)
@@ -70,11 +71,19 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache):
         T = x.shape[0]
-        qkv = self.qkv(x, ctx.ws.rows("qkv", T, self.n_qkv, self.dtype))
         pos = self.position
-        ops.rope_store(qkv, ctx.tok_pos, ctx.tok_entry, cache.block_table,
-                       cache.storage if cache.writable else None, cache.page_size,
-                       self.nh, self.nkv, self.hd, pos.rot_dim, pos.inv_freq, pos.mscale)
+        qkv = ctx.ws.rows("qkv", T, self.n_qkv, self.dtype)
+        store = cache.storage if cache.writable else None
+        if (self.dtype == torch.bfloat16 and self.fuse_rope
+                and ops.skinny_rope_ok(T, self.hidden, self.hd, pos.rot_dim)):
+            # a few rows (decode): the projection rotates q and k and writes k, v to the cache in its epilogue
+            ops.gemm_skinny_rope(x, self.qkv.weight, qkv, self.qkv.alpha, self.qkv.bias, ctx.tok_pos, ctx.tok_entry,
+                                 cache.block_table, store, cache.page_size, self.nh, self.nkv, self.hd, pos.rot_dim,
+                                 pos.inv_freq, pos.mscale)
+        else:
+            self.qkv(x, qkv)
+            ops.rope_store(qkv, ctx.tok_pos, ctx.tok_entry, cache.block_table, store, cache.page_size,
+                           self.nh, self.nkv, self.hd, pos.rot_dim, pos.inv_freq, pos.mscale)
         out = ctx.ws.rows("attn_out", T, self.nh * self.hd, self.dtype)
         self.attend(qkv, out, ctx, cache)
         return self.o_proj(out, ctx.ws.rows("branch", T, self.hidden, self.dtype))

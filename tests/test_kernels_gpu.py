@@ -150,6 +150,42 @@ def test_rope_store(cuda_device, dtype, nh, nkv, hd, rot):
     assert float(dc[~written].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (6, 3, 32, 32), (32, 2, 128, 128), (5, 1, 48, 16), (3, 3, 64, 32), (2, 2, 32, 0)])
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
+def test_gemm_skinny_rope(cuda_device, nh, nkv, hd, rot, M):
+    """The q/k/v projection with rotation and cache write in its epilogue against the two kernels it stands for
+    (projection, then rope_store): the same bits but for the last one of a rotated value, the same cache slots written,
+    nothing else touched."""
+    page, K = 16, 200
+    N = (nh + 2 * nkv) * hd
+    starts = [3 * i + (40 if i % 3 == 0 else 0) for i in range(M)]          # one token per request, at assorted positions
+    bt, cache = _paged_setup(M, [s + 1 for s in starts], nkv, hd, page, torch.bfloat16, 21)
+    g = torch.Generator().manual_seed(22)
+    x = (torch.randn(M, K, generator=g) * 0.5).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.1).bfloat16().cuda()
+    bias = torch.randn(N, generator=g).cuda() if (M % 2) else None
+    tok_pos, tok_entry = torch.tensor(starts, dtype=torch.int32).cuda(), torch.arange(M, dtype=torch.int32).cuda()
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(rot // 2, dtype=torch.float64) * 2 / max(rot, 1)))).float().cuda() if rot else None
+    mscale, alpha = 1.0931, 0.75
+    assert ops.skinny_rope_ok(M, K, hd, rot)
+    # the two kernels
+    ref_out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ref_cache = cache.clone().cuda()
+    ops.gemm_skinny(x, w, ref_out, alpha, bias)
+    ops.rope_store(ref_out, tok_pos, tok_entry, bt.cuda(), ref_cache, page, nh, nkv, hd, rot, inv_freq, mscale)
+    # the fused one
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    d_cache = cache.clone().cuda()
+    ops.gemm_skinny_rope(x, w, out, alpha, bias, tok_pos, tok_entry, bt.cuda(), d_cache, page, nh, nkv, hd, rot, inv_freq, mscale)
+    close(out.cpu(), ref_out.cpu(), "float32", scale=ref_out.float().abs().max().cpu() * 400)   # 2e-5 * 400: one bfloat16 step
+    close(d_cache.cpu(), ref_cache.cpu(), "float32", scale=ref_out.float().abs().max().cpu() * 400)
+    assert torch.equal(d_cache == 0, ref_cache == 0)                       # the same slots, no other
+    # and without a cache to write: the rows only
+    out2 = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_skinny_rope(x, w, out2, alpha, bias, tok_pos, tok_entry, bt.cuda(), None, page, nh, nkv, hd, rot, inv_freq, mscale)
+    assert torch.equal(out2, out)
+
+
 # -- attention -------------------------------------------------------------------------------------
 def _attn_reference(q, kc, bt, entry_of_tok, pos_of_tok, nh, nkv, hd, page, window):
     """q [T, nh, hd] f32; kc cache f32; returns [T, nh*hd]."""
