@@ -112,9 +112,11 @@ def _paged_setup(E, lens, nkv, hd, page, dtype, seed, n_extra_pages=3):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nh,nkv,hd,rot", [(4, 2, 16, 16), (5, 1, 48, 24), (6, 3, 32, 32), (3, 3, 80, 0)])
-def test_rope_store(cuda_device, dtype, nh, nkv, hd, rot):
+@pytest.mark.parametrize("many", [False, True])
+def test_rope_store(cuda_device, dtype, nh, nkv, hd, rot, many):
     page = 16
-    starts, qlens = [0, 30, 15], [5, 1, 20]
+    # a few tokens and many tokens go through two different kernels
+    starts, qlens = ([0, 30, 15], [5, 1, 20]) if not many else ([0, 30, 15], [45, 1, 70])
     lens = [s + q for s, q in zip(starts, qlens)]
     bt, cache = _paged_setup(3, lens, nkv, hd, page, DT[dtype], 4)
     T = sum(qlens)
