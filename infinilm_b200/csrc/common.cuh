@@ -67,6 +67,11 @@ __device__ __forceinline__ float il_block_max(float v, float* sh) {
     return t;
 }
 
+// SiLU(g) * u for the bfloat16 path: exponential and division by the fast units (relative error near 2^-21, far below a
+// bfloat16 step). The decode product's epilogue and the SwiGLU kernel both use it, so a token's activation does not
+// depend on which of the two computed it. The float32 path keeps expf and a true division.
+__device__ __forceinline__ float il_silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+
 // ---- programmatic dependent launch --------------------------------------------------------------
 // Kernels of the decode path are launched so that the next kernel in the stream may become resident
 // while this one drains (INFINILM_B200_PDL=0 turns it off). A kernel waits for its predecessor to have

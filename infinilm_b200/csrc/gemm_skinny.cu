@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __n
         float y = alpha * s0 + (bias ? bias[n] : 0.f);
         if (GLU) {
             const float u = alpha * s1 + (bias ? bias[N + n] : 0.f);
-            y = y / (1.f + expf(-y)) * u;
+            y = il_silu_mul_fast(y, u);
         }
         gs_store<TO>(out + (size_t)m * ldo + n, y);
     }

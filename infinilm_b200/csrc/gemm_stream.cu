@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_stream_kernel(const __nv_b
             float y = alpha * s0 + (bias ? bias[n] : 0.f);
             if (GLU) {
                 const float u = alpha * s1 + (bias ? bias[N + n] : 0.f);
-                y = y / (1.f + expf(-y)) * u;
+                y = il_silu_mul_fast(y, u);
             }
             gt_store<TO>(out + (size_t)m * ldo + n, y);
         }

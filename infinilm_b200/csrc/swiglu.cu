@@ -11,8 +11,7 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
         const int i = (int)(idx - t * I);
         const float g = il_to_f(gu[t * 2 * I + i]);
         const float u = il_to_f(gu[t * 2 * I + I + i]);
-        const float s = g / (1.f + expf(-g));
-        out[idx] = il_from_f<TA>(s * u);
+        out[idx] = il_from_f<TA>(sizeof(TA) == 2 ? il_silu_mul_fast(g, u) : g / (1.f + expf(-g)) * u);
     }
 }
 
@@ -34,7 +33,7 @@ __global__ void swiglu_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ ou
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
             const float g = il_to_f(gp[k]), u = il_to_f(up[k]);
-            op[k] = il_from_f<TA>(g / (1.f + expf(-g)) * u);
+            op[k] = il_from_f<TA>(sizeof(TA) == 2 ? il_silu_mul_fast(g, u) : g / (1.f + expf(-g)) * u);
         }
         *reinterpret_cast<uint4*>(out + t * I + i) = oq;
     }
