@@ -228,7 +228,7 @@ class Scheduler:
         decoding = [r for r in self.running if not r.closing and r.n_tokens - r.n_cached == 1]
         filling = [r for r in self.running if not r.closing and r.n_tokens - r.n_cached > 1]
         for r in sorted(decoding, key=lambda r: r.arrival) + sorted(filling, key=lambda r: r.arrival):
-            if r not in self.running:             # preempted a moment ago
+            if out.preempted and any(r is v for v in out.preempted):      # preempted a moment ago
                 continue
             if budget <= 0:
                 break
@@ -249,12 +249,14 @@ class Scheduler:
             out.entries.append(ScheduledEntry(r, toks, samples=(r.n_cached + len(toks) == r.n_tokens)))
 
         # 2. admissions, in arrival order; the first that does not fit stops the scan
+        promised = None                           # pages the running requests may still ask for (worst case), summed once
         while self.waiting and budget > 0 and len(self.running) < self.max_batch_size:
             r = self.waiting[0]
             toks = self._next_tokens(r, budget)
             need = self._pages(len(toks))
             if self.admission == "worst_case":
-                promised = sum(self._worst_case_left(x) for x in self.running)
+                if promised is None:
+                    promised = sum(self._worst_case_left(x) for x in self.running)
                 if promised + self._worst_case_left(r) > self._free_pages():
                     break
             if need > free:
@@ -266,6 +268,8 @@ class Scheduler:
             self.waiting.popleft()
             r.status = RequestStatus.RUNNING
             self.running.append(r)
+            if promised is not None:
+                promised += self._worst_case_left(r)
             free -= need
             budget -= len(toks)
             out.entries.append(ScheduledEntry(r, toks, samples=(len(toks) == r.n_tokens)))
