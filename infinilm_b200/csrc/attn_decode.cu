@@ -28,7 +28,7 @@ constexpr int AD_PAGE = 16;                       // keys per tile = page size t
 constexpr int AD_STAGES = 2;                      // 4 warps x 2 stages of a page (8-9 KB at head_dim 128): three blocks fit on an SM
 constexpr int AD_STAGE_BYTES = 2 * AD_PAGE * AT_ROW_BYTES;
 constexpr int AD_SMEM_PIPE = AD_WARPS * AD_STAGES * AD_STAGE_BYTES;
-constexpr int AD_SMEM_MERGE = AD_WARPS * 16 * (HEAD_DIM + 4 + 2) * 4;   // the warps' scaled outputs and their (m, l)
+constexpr int AD_SMEM_MERGE = (AD_WARPS * 16 * (HEAD_DIM + 4 + 2) + 16 * (HEAD_DIM + 2)) * 4;   // the warps' scaled outputs and (m, l); the block's result
 constexpr int AD_SMEM = (AD_SMEM_PIPE > AD_SMEM_MERGE ? AD_SMEM_PIPE : AD_SMEM_MERGE) + AD_WARPS * AD_STAGES * 8 + 1024;
 constexpr bool AD_TMA_OK = (HEAD_DIM % 64 == 0);
 constexpr int AD_BOXES = HEAD_DIM / 64;           // 64-column boxes of a K (or V) block
@@ -109,6 +109,31 @@ __device__ __forceinline__ void ad_merge_row(float* fs, const float* o_part, con
 // (qkv, and o_part / ml_part in the merge, are written by the kernel before and read after a wait that is not the
 // kernel's first statement: they are not declared __restrict__, so that no load of them is treated as read-only
 // data and scheduled above the wait.)
+// CLUSTER 1: the splits of one (request, kv head, row tile) are the blocks of one thread-block cluster (cluster size =
+// n_splits = gridDim.x, a power of two up to 16) and merge their partial results through distributed shared memory:
+// no partials in global memory and no second kernel. Every block of a cluster passes both cluster barriers, whatever
+// its share of pages (none included) and whatever its copies did.
+__device__ __forceinline__ void ad_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t ad_map_peer(const void* smem_ptr, uint32_t rank) {
+    uint32_t local = (uint32_t)__cvta_generic_to_shared(smem_ptr), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float4 ad_ld_peer4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 ad_ld_peer2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+
+template <int CLUSTER>
 __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const __nv_bfloat16* qkv, int row_stride, const __nv_bfloat16* __restrict__ cache,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
@@ -134,7 +159,10 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int p0 = first_page + split * pages_per_split;
     int p1 = p0 + pages_per_split;
     if (p1 > last_page + 1) p1 = last_page + 1;
-    if (p0 > last_page) return;                   // this split has no keys; the merge knows
+    if (p0 > last_page) {                         // this split has no keys
+        if (!CLUSTER) return;                     // the merge kernel knows
+        p1 = p0;                                  // in a cluster it goes along with nothing to add: the barriers want every block
+    }
 
     const int* bt = block_table + (size_t)e * bt_stride;
     const size_t page_elems = (size_t)2 * nkv * AD_PAGE * AT_HD;
@@ -310,6 +338,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     float* sm_ml = reinterpret_cast<float*>(smem);                     // [warp][16 rows][m, l]
     float* sm_o = sm_ml + AD_WARPS * 16 * 2;                           // [warp][16 rows][AT_HD + 4]
     constexpr int OS = AT_HD + 4;
+    float* res_ml = sm_o + AD_WARPS * 16 * OS;                         // [16 rows][m, l] of this block, for its cluster
+    float* res_o = res_ml + 16 * 2;                                    // [16 rows][AT_HD]
     if ((lane & 3) == 0) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -344,7 +374,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
             acc.w += v.w;
         }
         const size_t pr = ((size_t)e * nh + head0 + r) * n_splits + split;
-        *reinterpret_cast<float4*>(o_part + pr * AT_HD + d) = acc;
+        if (CLUSTER) *reinterpret_cast<float4*>(res_o + (size_t)r * AT_HD + d) = acc;
+        else *reinterpret_cast<float4*>(o_part + pr * AT_HD + d) = acc;
         if (d == 0) {
             float M = -INFINITY, L = 0.f;
 #pragma unroll
@@ -354,9 +385,48 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
                 const float mw = sm_ml[(w * 16 + r) * 2];
                 L += ((mw == -INFINITY) ? 0.f : exp2f(mw - M)) * sm_ml[(w * 16 + r) * 2 + 1];
             }
-            ml_part[pr * 2] = M;
-            ml_part[pr * 2 + 1] = L;
+            if (CLUSTER) {
+                res_ml[r * 2] = M;
+                res_ml[r * 2 + 1] = L;
+            } else {
+                ml_part[pr * 2] = M;
+                ml_part[pr * 2 + 1] = L;
+            }
         }
+    }
+    if (CLUSTER) {
+        // The cluster's blocks hold one partial result each. Block `split` merges rows split, split + n_splits, ...: a
+        // warp a row, lanes over the peers for (m, l), then over the columns, every peer's four values asked for at once.
+        __syncthreads();
+        ad_cluster_sync();
+        for (int r = split + warp * n_splits; r < rows_valid; r += n_splits * AD_WARPS) {
+            float2 mlp = make_float2(-INFINITY, 0.f);
+            if (lane < n_splits) mlp = ad_ld_peer2(ad_map_peer(res_ml + r * 2, (uint32_t)lane));
+            const float M = il_warp_max(mlp.x);
+            const float f = (mlp.x == -INFINITY) ? 0.f : exp2f(mlp.x - M);
+            const float inv = 1.f / il_warp_sum(f * mlp.y);
+            float fp[16];                         // every lane gets every peer's factor here, with the whole warp present:
+#pragma unroll
+            for (int p = 0; p < 16; ++p) fp[p] = __shfl_sync(0xffffffffu, f, p);   // (the column loop below is not: lanes past head_dim / 4 skip it)
+            for (int d = lane * 4; d < AT_HD; d += 128) {
+                float4 v[16];
+#pragma unroll
+                for (int p = 0; p < 16; ++p)
+                    v[p] = p < n_splits ? ad_ld_peer4(ad_map_peer(res_o + (size_t)r * AT_HD + d, (uint32_t)p)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int p = 0; p < 16; ++p) {    // in split order
+                    acc.x += fp[p] * v[p].x;
+                    acc.y += fp[p] * v[p].y;
+                    acc.z += fp[p] * v[p].z;
+                    acc.w += fp[p] * v[p].w;
+                }
+                const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
+                *reinterpret_cast<uint2*>(out + ((size_t)e * nh + head0 + r) * AT_HD + d) = make_uint2(a, b);
+            }
+        }
+        ad_cluster_sync();                        // no block leaves while a peer may still read its results
+        return;
     }
     if (!counters) return;                        // the merge runs as a kernel of its own
 
@@ -405,20 +475,47 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
 static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
                      const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
                      int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
-                     int* status = nullptr, int* counters = nullptr) {
+                     int* status = nullptr, int* counters = nullptr, int cluster = 0) {
     static CUtensorMap no_map;                    // passed when there is no map: the kernel does not look at it
     const int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
     static bool attr_set[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return 1000 + (int)e;
         attr_set[dev] = true;
     }
     const int G = nh / nkv, row_tiles = (G + 15) / 16;
     dim3 grid(n_splits, nkv * row_tiles, n_decode);
-    IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, AD_SMEM, stream,
+    if (cluster) {
+        // one cluster per (request, kv head, row tile): its blocks are the splits
+        if (n_splits > 16 || (n_splits & (n_splits - 1))) return IL_BAD_ARG;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(AD_WARPS * 32);
+        cfg.dynamicSmemBytes = AD_SMEM;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)n_splits;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = il_pdl_enabled() ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<1>, (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache,
+                                           block_table, bt_stride, entry_kvlen, nh, nkv, scale * 1.4426950408889634f, window, pages_per_split,
+                                           n_splits, (float*)nullptr, (float*)nullptr, use_tma ? *kv_map : no_map, use_tma, status,
+                                           (int*)nullptr, (__nv_bfloat16*)out);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        IL_LAUNCH_CHECK();
+        return IL_OK;
+    }
+    IL_LAUNCH(attn_decode_kernel<0>, grid, AD_WARPS * 32, AD_SMEM, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
         scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, use_tma, status, counters, (__nv_bfloat16*)out);
     if (counters) return IL_OK;                   // merged by the last block of each group of splits
@@ -429,17 +526,47 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     return IL_OK;
 }
 
+// The largest cluster (16, 8, 4, 2 or 1 blocks) of the cluster form that this device can hold at once with this head size,
+// from the occupancy calculator; 0 if the query fails.
+IL_EXPORT int il_attn_decode_cluster_max() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (cached[dev]) return cached[dev] < 0 ? 0 : cached[dev];
+    cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
+    cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    int best = -1;
+    for (int s = 16; s >= 1 && best < 0; s >>= 1) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(s, 1, 1);
+        cfg.blockDim = dim3(AD_WARPS * 32);
+        cfg.dynamicSmemBytes = AD_SMEM;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)s;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel<1>, &cfg) == cudaSuccess && n > 0) best = s;
+    }
+    cudaGetLastError();
+    cached[dev] = best;
+    return best < 0 ? 0 : best;
+}
+
 // Scratch the caller provides: o_part float32 [n_decode * nh * n_splits * head_dim], ml_part [n_decode * nh * n_splits * 2].
 IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                              int bt_stride, const int* entry_kvlen, int page_size, int n_decode, int nh, int nkv, int hd,
                              float scale, int window, int pages_per_split, int n_splits, float* o_part, float* ml_part,
-                             const void* kv_map, int* status, int* counters, cudaStream_t stream) {
+                             const void* kv_map, int* status, int* counters, int cluster, cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
     return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
-                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, counters);
+                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, counters, cluster);
 }
 
 // Writes a tensor map (128 bytes at `out_map`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16 seen as

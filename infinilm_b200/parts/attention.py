@@ -37,6 +37,10 @@ class Attention(Mixer):
         self.force_plain = bool(p.get("plain_kernel", False))
         self.prefill_kernel = str(p.get("prefill_kernel", os.environ.get("INFINILM_B200_PREFILL_ATTN", "auto")))   # "mma": never tcgen05
         self.fuse_rope = os.environ.get("INFINILM_B200_FUSE_ROPE", "1") != "0"
+        # The splits of a request and kv head can run as one thread-block cluster that merges through distributed shared
+        # memory (INFINILM_B200_ATTN_CLUSTER = largest cluster, 2..16). Off: the 8B decode step at batch 8 measured 3.62 ms
+        # with clusters of 16, 3.56 with 8, against 3.29 ms with the merge as a kernel of its own.
+        self.cluster_merge = int(os.environ.get("INFINILM_B200_ATTN_CLUSTER", "0"))
         self.scale = 1.0 / math.sqrt(self.hd)
         self.n_qkv = (self.nh + 2 * self.nkv) * self.hd
         self.qkv = Linear(self.hidden, self.n_qkv, dtype)
@@ -110,11 +114,20 @@ class Attention(Mixer):
             base = n_dec * self.nkv * ((G + 15) // 16)
             # as many splits as fill one wave of blocks (two per SM), never more: a second, part-filled wave costs more
             n_splits = max(1, min(self.TARGET_BLOCKS // base, (max_pages + 3) // 4, 128))
-            rows = n_dec * self.nh * n_splits
-            ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
-                                 self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
-                                 ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
-                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map)
+            cluster_max = min(self.cluster_merge, ops.attention_decode_cluster_max(self.hd)) if self.cluster_merge else 0
+            if cluster_max > 0:
+                # the splits of a request and kv head as one thread-block cluster that merges its own partial results:
+                # a power of two, as many as the device holds in one cluster (up to 16)
+                n_splits = min(cluster_max, 1 << (n_splits.bit_length() - 1))
+                ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
+                                     self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits, None, None,
+                                     kv_map=cache.tma_map, cluster=True)
+            else:
+                rows = n_dec * self.nh * n_splits
+                ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
+                                     self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
+                                     ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
+                                     ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map)
             # (the kernel can also merge the splits itself, in the last block of each group - `counters=` - but the
             # merge as a second, wide launch measured faster: 3.7 against 3.9 ms for the 8B decode step at batch 8)
         if E > n_dec:

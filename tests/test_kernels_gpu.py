@@ -309,6 +309,28 @@ def test_attention_prefill_tc5_late_maximum(cuda_device):
 
 @pytest.mark.parametrize("nh,nkv,hd", SHAPES)
 @pytest.mark.parametrize("window", [None, 40])
+@pytest.mark.parametrize("splits", [1, 2, 4, 8, 16])
+def test_attention_decode_cluster(cuda_device, nh, nkv, hd, window, splits):
+    """The splits of a request and kv head as one thread-block cluster that merges through distributed shared memory:
+    requests of one page (most blocks of their cluster have no key) beside requests of many."""
+    assert ops.attention_decode_cluster_max(hd) >= 8                        # up to 8 is the portable cluster size
+    if splits > ops.attention_decode_cluster_max(hd):
+        pytest.skip("this device does not hold a cluster of 16 such blocks")
+    starts = [0, 15, 16, 200, 63, 64, 700]
+    c = _attn_case("bfloat16", nh, nkv, hd, starts, [1] * len(starts), window, 13, dominate=True)
+    E = c["E"]
+    kv_map = ops.kv_tensor_map(c["cache"])
+    for m in ([None] if kv_map is None else [None, kv_map]):
+        out = torch.full((E, nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
+                             window, 0, splits, None, None, kv_map=m, cluster=True)
+        torch.cuda.synchronize()
+        ops.check_status("cuda:0")
+        close(out.cpu(), c["ref"], "bfloat16")
+
+
+@pytest.mark.parametrize("nh,nkv,hd", SHAPES)
+@pytest.mark.parametrize("window", [None, 40])
 @pytest.mark.parametrize("splits", [1, 3, 7])
 def test_attention_decode_bf16(cuda_device, nh, nkv, hd, window, splits):
     starts = [0, 15, 16, 200, 63, 64]
