@@ -112,8 +112,8 @@ def weight_bytes(cfg, n_layers):
 
 
 def profile_step(args) -> int:
-    """One decode step (batch --batch, 2,048 tokens cached) or one 2,048-token prefill step of the benchmark
-    model with --layers layers, bracketed by cudaProfilerStart/Stop; nothing is timed or printed but 'profiled'."""
+    """One decode step (batch --batch, --prompt-len tokens cached) or one prefill step (the last 2,048 tokens of a
+    --prompt-len prompt) of the benchmark model with --layers layers, bracketed by cudaProfilerStart/Stop; nothing is timed or printed but 'profiled'."""
     import torch
 
     from infinilm_b200.config import config_from_json
@@ -122,15 +122,22 @@ def profile_step(args) -> int:
     raw = dict(CONFIG_8B)
     raw["num_hidden_layers"] = args.layers or 2
     cfg = config_from_json(raw)
-    B = args.batch
+    B, P = args.batch, args.prompt_len
+    if P % PROMPT_LEN or P <= 0 or P + 16 > cfg.max_position_embeddings:
+        print(f"--prompt-len must be a positive multiple of {PROMPT_LEN} below the model's maximum")
+        return 2
     eng = Engine.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", page_size=PAGE,
-                              num_pages=B * (PROMPT_LEN // PAGE + 4) + 8, max_seqs=max(B, 2), max_batch_tokens=4096)
+                              num_pages=B * (P // PAGE + 4) + 8, max_seqs=max(B, 2), max_batch_tokens=4096)
     g = torch.Generator().manual_seed(1)
-    prompts = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in range(B)]
+    prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=g).tolist() for _ in range(B)]
+
+    def feed(seq, ids, upto):                     # a prompt's tokens [0, upto) in portions of 2,048, nothing wanted
+        for a in range(0, upto, PROMPT_LEN):
+            eng.step([StepEntry(seq, ids[a:a + PROMPT_LEN], [])])
     if args.profile_step == "decode":
         seqs = [eng.open(i) for i in range(B)]
         for s, p in zip(seqs, prompts):
-            eng.step([StepEntry(s, p, [])])
+            feed(s, p, P)
         for _ in range(2):
             eng.step([StepEntry(s, [5], [0]) for s in seqs])
         torch.cuda.synchronize()
@@ -138,15 +145,16 @@ def profile_step(args) -> int:
         eng.step([StepEntry(s, [5], [0]) for s in seqs])
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
-    else:
+    else:                                         # the last portion of the prompt, over the cache of the others
         for i in range(2):
             s = eng.open(("w", i))
-            eng.step([StepEntry(s, prompts[0], [PROMPT_LEN - 1])])
+            feed(s, prompts[0], P)
             eng.close(s)
+        s = eng.open("p")
+        feed(s, prompts[0], P - PROMPT_LEN)
         torch.cuda.synchronize()
         torch.cuda.profiler.start()
-        s = eng.open("p")
-        eng.step([StepEntry(s, prompts[0], [PROMPT_LEN - 1])])
+        eng.step([StepEntry(s, prompts[0][P - PROMPT_LEN:], [PROMPT_LEN - 1])])
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
     print("profiled")

@@ -44,6 +44,11 @@ __device__ __forceinline__ bool ad_mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
+// One page of one kv head, K and V, all of head_dim: a box of a five-dimensional view of the cache (see il_attn_decode_kv_map).
+__device__ __forceinline__ void ad_tma_page(uint32_t dst, const CUtensorMap* map, int g, int page, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %4, %5}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(g), "r"(page * 2) : "memory");
+}
 __device__ __forceinline__ void ad_tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
@@ -138,7 +143,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const __nv_bfloat16* qkv, int row_stride, const __nv_bfloat16* __restrict__ cache,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
-    float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, int use_tma, int* __restrict__ status,
+    float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap kv_page_map,
+    int use_tma, int* __restrict__ status,
     int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -199,11 +205,15 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
                 const uint32_t st = tpipe + (it % AD_STAGES) * AD_TMA_STAGE_BYTES, bar = tbars + (it % AD_STAGES) * 8;
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the tile was read by ldmatrix before
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(AD_TMA_STAGE_BYTES) : "memory");
-                const int rk = ((page * 2) * nkv + g) * AD_PAGE, rv = ((page * 2 + 1) * nkv + g) * AD_PAGE;
+                if (use_tma == 2) {               // the whole page in one copy: copies of 2 KB keep the copy engine below the memory's rate
+                    ad_tma_page(st, &kv_page_map, g, page, bar);
+                } else {
+                    const int rk = ((page * 2) * nkv + g) * AD_PAGE, rv = ((page * 2 + 1) * nkv + g) * AD_PAGE;
 #pragma unroll
-                for (int bx = 0; bx < AD_BOXES; ++bx) {
-                    ad_tma_2d(st + bx * 2048, &kv_map, bx * 64, rk, bar);
-                    ad_tma_2d(st + (AD_BOXES + bx) * 2048, &kv_map, bx * 64, rv, bar);
+                    for (int bx = 0; bx < AD_BOXES; ++bx) {
+                        ad_tma_2d(st + bx * 2048, &kv_map, bx * 64, rk, bar);
+                        ad_tma_2d(st + (AD_BOXES + bx) * 2048, &kv_map, bx * 64, rv, bar);
+                    }
                 }
             }
         }
@@ -477,7 +487,13 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
                      int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
                      int* status = nullptr, int* counters = nullptr, int cluster = 0) {
     static CUtensorMap no_map;                    // passed when there is no map: the kernel does not look at it
-    const int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
+    int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
+    if (use_tma) {                                // a second map may follow the first: the page view (all zero: there is none)
+        const unsigned char* second = reinterpret_cast<const unsigned char*>(kv_map + 1);
+        for (size_t i = 0; i < sizeof(CUtensorMap) && use_tma == 1; ++i)
+            if (second[i]) use_tma = 2;
+    }
+    const CUtensorMap& page_map = use_tma == 2 ? kv_map[1] : no_map;
     static bool attr_set[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -509,7 +525,7 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
         cfg.numAttrs = il_pdl_enabled() ? 2 : 1;
         cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<1>, (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache,
                                            block_table, bt_stride, entry_kvlen, nh, nkv, scale * 1.4426950408889634f, window, pages_per_split,
-                                           n_splits, (float*)nullptr, (float*)nullptr, use_tma ? *kv_map : no_map, use_tma, status,
+                                           n_splits, (float*)nullptr, (float*)nullptr, use_tma ? *kv_map : no_map, page_map, use_tma, status,
                                            (int*)nullptr, (__nv_bfloat16*)out);
         if (e != cudaSuccess) return 1000 + (int)e;
         IL_LAUNCH_CHECK();
@@ -517,7 +533,7 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     }
     IL_LAUNCH(attn_decode_kernel<0>, grid, AD_WARPS * 32, AD_SMEM, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
-        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, use_tma, status, counters, (__nv_bfloat16*)out);
+        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status, counters, (__nv_bfloat16*)out);
     if (counters) return IL_OK;                   // merged by the last block of each group of splits
     const int n_rows = n_decode * nh;
     IL_LAUNCH(attn_decode_merge_kernel, (n_rows + 3) / 4, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window, pages_per_split,
@@ -569,10 +585,13 @@ IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const v
                      pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, counters, cluster);
 }
 
-// Writes a tensor map (128 bytes at `out_map`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16 seen as
-// rows of head_dim, for boxes of [16 rows x 64 columns] with the 128-byte swizzle. Returns 0, or IL_UNSUPPORTED.
-IL_EXPORT int il_attn_decode_kv_map(void* out_map, const void* cache, long long n_rows, int hd) {
-    if (!AD_TMA_OK || hd != HEAD_DIM || ((uintptr_t)cache & 15)) return IL_UNSUPPORTED;
+// Writes two tensor maps (2 x 128 bytes at `out_maps`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16:
+// first the cache seen as rows of head_dim, for boxes of [16 rows x 64 columns] with the 128-byte swizzle; then a view
+// with the dimensions (64 columns, 16 slots, head_dim / 64 column blocks, kv heads, 2 * pages) whose box is one page
+// of one kv head, K and V: it lands in shared memory as the same 2 KB tiles, [K, V][column block][slot][64]. The second
+// is all zero if the driver does not take it. n_rows = pages * 2 * kv heads * 16. Returns 0, or IL_UNSUPPORTED.
+IL_EXPORT int il_attn_decode_kv_map(void* out_maps, const void* cache, long long n_rows, int hd, int nkv) {
+    if (!AD_TMA_OK || hd != HEAD_DIM || nkv <= 0 || ((uintptr_t)cache & 15)) return IL_UNSUPPORTED;
     typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -584,15 +603,30 @@ IL_EXPORT int il_attn_decode_kv_map(void* out_map, const void* cache, long long 
             return IL_UNSUPPORTED;
         enc = (encode_fn)p;
     }
-    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)n_rows};
-    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)AD_PAGE};
-    cuuint32_t estr[2] = {1, 1};
-    CUtensorMap m;
-    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return 2000 + (int)r;
-    memcpy(out_map, &m, sizeof(m));
+    CUtensorMap m[2];
+    memset(m, 0, sizeof(m));
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)n_rows};
+        cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)AD_PAGE};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = enc(&m[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return 2000 + (int)r;
+    }
+    {
+        const cuuint64_t n_kvpages = (cuuint64_t)(n_rows / ((long long)nkv * AD_PAGE));
+        cuuint64_t dims[5] = {64, (cuuint64_t)AD_PAGE, (cuuint64_t)(hd / 64), (cuuint64_t)nkv, n_kvpages};
+        cuuint64_t strides[4] = {(cuuint64_t)hd * 2, 128, (cuuint64_t)AD_PAGE * hd * 2, (cuuint64_t)nkv * AD_PAGE * hd * 2};
+        cuuint32_t box[5] = {64, (cuuint32_t)AD_PAGE, (cuuint32_t)(hd / 64), 1, 2};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUtensorMap t;
+        CUresult r = enc(&t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS) m[1] = t;          // else: stays zero, the kernel copies 2 KB boxes
+    }
+    memcpy(out_maps, m, sizeof(m));
     return IL_OK;
 }

@@ -286,8 +286,8 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
         n_cnt = n_decode * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
         if not counters.is_cuda or counters.dtype != torch.int32 or counters.numel() < n_cnt:
             raise KernelError("attention_decode: counters must be int32 on the device, one per (row, kv head, head tile)")
-    if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != 128):
-        raise KernelError("attention_decode: kv_map must be the 128-byte host tensor kv_tensor_map returned")
+    if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != 256):
+        raise KernelError("attention_decode: kv_map must be the 256-byte host tensor kv_tensor_map returned")
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
@@ -312,16 +312,17 @@ def attention_decode_cluster_max(head_dim: int) -> int:
 
 
 def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:
-    """A TMA tensor map (128 bytes, on the host) of one layer's bfloat16 cache [pages,2,kv_heads,16,head_dim], or
-    None when the decode attention kernel has no tensor-copy path for this geometry (head_dim not a multiple of 64)."""
+    """The TMA tensor maps (2 x 128 bytes, on the host) of one layer's bfloat16 cache [pages,2,kv_heads,16,head_dim]: one
+    for boxes of [16 keys x 64 columns], one whose box is a whole page of a kv head (all zero if the driver refuses it).
+    None when the attention kernels have no tensor-copy path for this geometry (head_dim not a multiple of 64)."""
     if not cache.is_cuda or cache.dtype != torch.bfloat16 or cache.dim() != 5 or cache.shape[3] != 16 or cache.shape[4] % 64:
         return None
     hd = cache.shape[4]
     lib = build.load("attn_decode", {"HEAD_DIM": hd})
     fn = lib.il_attn_decode_kv_map
-    fn.argtypes, fn.restype = [_c_void_p, _c_void_p, ctypes.c_longlong, _c_int], _c_int
-    m = torch.zeros(128, dtype=torch.uint8)
-    rc = fn(_c_void_p(m.data_ptr()), _ptr(cache), cache.numel() // hd, hd)
+    fn.argtypes, fn.restype = [_c_void_p, _c_void_p, ctypes.c_longlong, _c_int, _c_int], _c_int
+    m = torch.zeros(256, dtype=torch.uint8)
+    rc = fn(_c_void_p(m.data_ptr()), _ptr(cache), cache.numel() // hd, hd, cache.shape[2])
     return m if rc == 0 else None
 
 
