@@ -17,7 +17,9 @@
 //   Roles by warp: 0 producer (TMA; K and V each in a ring of two slots, K freed as soon as its scores are computed,
 //   V when its product is), 1 tensor-core issue and tensor-memory allocation, 2-5 softmax and output. 256 columns of
 //   tensor memory and about 98 KB of shared memory: two blocks per SM, one's products under the other's softmax.
-//   (Two softmax threads a row, each with half the columns, measured slower: 71 against 53 us at 2,048 tokens.)
+//   (Two softmax threads a row, each with half the columns, measured slower: 71 against 53 us at 2,048 tokens. So did one
+//   block per SM that owns two tiles of 128 rows, loads the keys once for both and issues the products of both in
+//   turn: 67 us - its two softmax groups run in step and meet at the exponential unit, where two blocks drift apart.)
 //
 //   Pages past the entry's last page are read as the last page again (finite values the mask removes).
 //   Every mbarrier wait is bounded; one that runs out sets *status and all roles leave their loops.
@@ -320,11 +322,11 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
     }
 }
 
-// Rows a block owns: a tile is 128 / (heads per kv head) tokens.
+// Rows a block owns: it takes rows / (heads per kv head) consecutive tokens.
 IL_EXPORT int il_attn_prefill_tc5_rows() { return PT_ROWS; }
 
 // kv_map: the 128 bytes of the cache's tensor map (boxes of [16 rows x 64 columns], 128-byte swizzle), on the host.
-// n_tiles_total: sum over entries [first_entry, n_entries) of ceil(q_len / tpt), tpt = max(1, 128 / (nh/nkv)).
+// n_tiles_total: sum over entries [first_entry, n_entries) of ceil(q_len / tpt), tpt = max(1, rows / (nh/nkv)), rows = il_attn_prefill_tc5_rows().
 IL_EXPORT int il_attn_prefill_tc5(const void* qkv, int row_stride, void* out, const void* kv_map, const int* block_table,
                                   int bt_stride, const int* entry_qstart, const int* entry_kvlen, int page_size, int first_entry,
                                   int n_entries, int n_tiles_total, int nh, int nkv, int hd, float scale, int window, int* status,

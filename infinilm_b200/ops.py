@@ -346,12 +346,22 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
              int(window or 0), _stream()), "attention_prefill")
 
 
-TC5_PREFILL_ROWS = 128
+_tc5_prefill_rows = {}
+
+
+def prefill_tc5_rows(head_dim: int) -> int:
+    """Rows (tokens x heads of a kv head) a block of the tensor-memory prefill kernel owns."""
+    if head_dim not in _tc5_prefill_rows:
+        lib = build.load("attn_prefill_tc5", {"HEAD_DIM": head_dim})
+        fn = lib.il_attn_prefill_tc5_rows
+        fn.argtypes, fn.restype = [], _c_int
+        _tc5_prefill_rows[head_dim] = int(fn())
+    return _tc5_prefill_rows[head_dim]
 
 
 def prefill_tc5_ok(head_dim: int, group: int, page_size: int) -> bool:
     """Whether the tensor-memory prefill kernel takes this geometry (the caller also needs the cache's tensor map)."""
-    return head_dim in (64, 128) and 0 < group <= TC5_PREFILL_ROWS and page_size == 16
+    return head_dim in (64, 128) and 0 < group <= 128 and page_size == 16
 
 
 def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Tensor, block_table: torch.Tensor,
@@ -359,7 +369,7 @@ def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Te
                           n_tiles_total: int, page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                           window: Optional[int]) -> None:
     """The same attention as `attention_prefill`, on tcgen05 tensor cores with tensor memory; `kv_map` is the cache's
-    tensor map (`kv_tensor_map`). n_tiles_total = sum over the entries of ceil(q_len / (128 // (heads/kv_heads)))."""
+    tensor map (`kv_tensor_map`). n_tiles_total = sum over the entries of ceil(q_len / (prefill_tc5_rows(head_dim) // (heads/kv_heads)))."""
     _need_cuda(qkv, out, block_table, entry_qstart, entry_kvlen)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc5: bfloat16 tensors")

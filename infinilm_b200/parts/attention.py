@@ -135,7 +135,7 @@ class Attention(Mixer):
             # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.
             tc5 = (self.prefill_kernel != "mma" and cache.tma_map is not None
                    and ops.prefill_tc5_ok(self.hd, G, cache.page_size))
-            tpt = max(1, (ops.TC5_PREFILL_ROWS if tc5 else 64) // G)
+            tpt = max(1, (ops.prefill_tc5_rows(self.hd) if tc5 else 64) // G)
             n_tiles = sum((q + tpt - 1) // tpt for q in ctx.h_qlen[n_dec:])
             if tc5:
                 ops.attention_prefill_tc5(qkv, out, cache.tma_map, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,

@@ -271,7 +271,7 @@ def test_attention_prefill_tc5(cuda_device, nh, nkv, hd, window):
     for starts, qlens in [([0, 47, 16, 3], [33, 2, 17, 2]), ([0], [130]), ([100, 0], [70, 65]), ([5], [420])]:
         c = _attn_case("bfloat16", nh, nkv, hd, starts, qlens, window, 11, dominate=True)
         out = torch.full((c["T"], nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
-        tpt = max(1, ops.TC5_PREFILL_ROWS // G)
+        tpt = max(1, ops.prefill_tc5_rows(hd) // G)
         n_tiles = sum((q + tpt - 1) // tpt for q in qlens)
         kv_map = ops.kv_tensor_map(c["cache"])
         assert kv_map is not None
@@ -298,7 +298,7 @@ def test_attention_prefill_tc5_late_maximum(cuda_device):
         ref = _attn_reference(qkv.float().view(T, -1, hd)[:, :nh], cache.float(), bt, tok_entry, tok_pos, nh, nkv, hd, 16, None)
         out = torch.full((T, nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
         d_cache = cache.cuda()
-        tpt = ops.TC5_PREFILL_ROWS // (nh // nkv)
+        tpt = ops.prefill_tc5_rows(hd) // (nh // nkv)
         ops.attention_prefill_tc5(qkv.cuda(), out, ops.kv_tensor_map(d_cache), bt.cuda(), torch.tensor([0, T], dtype=torch.int32).cuda(),
                                   torch.tensor([T], dtype=torch.int32).cuda(), 0, 1, (T + tpt - 1) // tpt, 16, nh, nkv, hd,
                                   1 / math.sqrt(hd), None)
