@@ -70,7 +70,7 @@ __device__ __forceinline__ float il_block_max(float v, float* sh) {
 // SiLU(g) * u for the bfloat16 path: exponential and division by the fast units (relative error near 2^-21, far below a
 // bfloat16 step). The decode product's epilogue and the SwiGLU kernel both use it, so a token's activation does not
 // depend on which of the two computed it. The float32 path keeps expf and a true division.
-__device__ __forceinline__ float il_silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+__device__ __forceinline__ float il_silu_mul_fast(float g, float u) { return __fmul_rn(__fdividef(g, __fadd_rn(1.f, __expf(-g))), u); }
 
 // ---- programmatic dependent launch --------------------------------------------------------------
 // Kernels of the decode path are launched so that the next kernel in the stream may become resident

@@ -196,9 +196,9 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_stream_kernel(const __nv_b
                 s0 += p[w][tt][nl][mc];
                 if (GLU) s1 += p[w][tt][nl + 8][mc];
             }
-            float y = alpha * s0 + (bias ? bias[n] : 0.f);
+            float y = __fmaf_rn(alpha, s0, bias ? bias[n] : 0.f);      // spelled out: the same bits as gemm_skinny's epilogue
             if (GLU) {
-                const float u = alpha * s1 + (bias ? bias[N + n] : 0.f);
+                const float u = __fmaf_rn(alpha, s1, bias ? bias[N + n] : 0.f);
                 y = il_silu_mul_fast(y, u);
             }
             gt_store<TO>(out + (size_t)m * ldo + n, y);

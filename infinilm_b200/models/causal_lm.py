@@ -64,7 +64,13 @@ class CausalLM:
         self.embedding.forward(ctx.token_ids, resid)
         pending = None
         for i, st in enumerate(self.order):
-            pending = self.blocks[st.layer].run(resid, pending, ctx, caches[i])
+            # the block that runs next may take its first norm half done (its weights applied, the rms still to divide by)
+            blk = self.blocks[st.layer]
+            nxt = self.blocks[self.order[i + 1].layer] if i + 1 < len(self.order) else None
+            if blk.takes_next_norm and nxt is not None and nxt.accepts_normed_input(T):
+                pending = blk.run(resid, pending, ctx, caches[i], next_norm=nxt.mixer_norm)
+            else:
+                pending = blk.run(resid, pending, ctx, caches[i])
             if ctx.tap is not None:
                 ctx.tap(f"layer{i}", resid, pending)
         n = ctx.n_want

@@ -387,10 +387,37 @@ def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Te
 SKINNY_MAX_ROWS = 16
 
 
+class NormedInput:
+    """Activations whose RMSNorm is not finished: `xw` = residual * norm weight (bfloat16 [T,H]) and `sumsq`, the sums of
+    the residual's squares per row and block of 16 columns (float32 [T, n_blocks]); the product that reads them divides
+    by the rms. Made by `gemm_skinny_resid`, read by `gemm_skinny(glu=True)` and `gemm_skinny_rope`."""
+    __slots__ = ("xw", "sumsq", "width", "eps")
+
+    def __init__(self, xw: torch.Tensor, sumsq: torch.Tensor, width: int, eps: float):
+        self.xw, self.sumsq, self.width, self.eps = xw, sumsq, int(width), float(eps)
+
+    @property
+    def shape(self):
+        return self.xw.shape
+
+
+NORM_MAX_BLOCKS = 256                             # blocks of 16 columns the fused norm handles: residual width <= 4096
+
+
+def _norm_args(norm_in: Optional[NormedInput], M: int):
+    if norm_in is None:
+        return _c_void_p(0), 0, 0, 0.0
+    sq = norm_in.sumsq
+    if sq.dtype != torch.float32 or not sq.is_contiguous() or sq.shape[0] < M or sq.shape[1] > NORM_MAX_BLOCKS:
+        raise KernelError("norm_in: sumsq float32 [rows, blocks <= 256], contiguous")
+    return _ptr(sq), sq.shape[1], norm_in.width, norm_in.eps
+
+
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
-                bias: Optional[torch.Tensor] = None, glu: bool = False) -> None:
+                bias: Optional[torch.Tensor] = None, glu: bool = False, norm_in: Optional[NormedInput] = None) -> None:
     """out[M,N] = alpha * x[M,K] @ w[N,K]^T (+ bias) for M <= 16 bfloat16 rows; out bfloat16 or float32.
-    glu: w is [2N,K] (gate rows, then up rows) and out[M,N] = silu(gate) * up."""
+    glu: w is [2N,K] (gate rows, then up rows) and out[M,N] = silu(gate) * up.
+    norm_in (glu only): x is `norm_in.xw`, and the results are divided by the rms that its sums give."""
     _need_cuda(x, w, out, bias)
     M, K = x.shape
     N = w.shape[0] // 2 if glu else w.shape[0]
@@ -400,10 +427,47 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: floa
         raise KernelError("gemm_skinny: innermost dimension must be contiguous")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.shape[0]):
         raise KernelError("gemm_skinny: bias float32, one per weight row")
+    if norm_in is not None and not glu:
+        raise KernelError("gemm_skinny: norm_in goes with glu=True (or gemm_skinny_rope)")
     f = _fn("gemm_skinny", "il_gemm_skinny", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p,
-                                              _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p])
+                                              _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_float,
+                                              _c_void_p])
+    np_, nb, nw, ne = _norm_args(norm_in, M)
     _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), kind_of(out.dtype), out.stride(0), _ptr(bias), alpha,
-             M, N, K, int(glu), _stream()), "gemm_skinny")
+             M, N, K, int(glu), np_, nb, nw, ne, _stream()), "gemm_skinny")
+
+
+def skinny_resid_ok(M: int, K: int, width: int) -> bool:
+    """Whether `gemm_skinny_resid` takes this shape."""
+    return 0 < M <= SKINNY_MAX_ROWS and K % 8 == 0 and (width + 15) // 16 <= NORM_MAX_BLOCKS
+
+
+def gemm_skinny_resid(x: torch.Tensor, w: torch.Tensor, alpha: float, bias: Optional[torch.Tensor], resid: torch.Tensor,
+                      branch_scale: float, norm_weight: torch.Tensor, eps: float, xw: torch.Tensor,
+                      sumsq: torch.Tensor) -> NormedInput:
+    """The last product of a branch (up to 16 bfloat16 rows) with the residual add and the next RMSNorm's inputs in its
+    epilogue: resid (float32 [M,H], in place) += branch_scale * bf16(alpha * x @ w^T + bias); xw = resid * norm_weight;
+    sumsq[m][b] = sum of resid[m]^2 over columns 16b..16b+15. Returns what the next product needs to finish the norm."""
+    _need_cuda(x, w, bias, resid, norm_weight, xw, sumsq)
+    M, K = x.shape
+    H = w.shape[0]
+    nb = (H + 15) // 16
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise KernelError(f"gemm_skinny_resid: bfloat16 x{tuple(x.shape)} w{tuple(w.shape)}")
+    if resid.dtype != torch.float32 or tuple(resid.shape) != (M, H) or xw.dtype != torch.bfloat16 or tuple(xw.shape) != (M, H):
+        raise KernelError("gemm_skinny_resid: resid float32 [M,H], xw bfloat16 [M,H]")
+    if sumsq.dtype != torch.float32 or tuple(sumsq.shape) != (M, nb) or norm_weight.numel() != H:
+        raise KernelError("gemm_skinny_resid: sumsq float32 [M, ceil(H/16)], norm_weight [H]")
+    if x.stride(1) != 1 or w.stride(1) != 1:
+        raise KernelError("gemm_skinny_resid: innermost dimension must be contiguous")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != H):
+        raise KernelError("gemm_skinny_resid: bias float32 [H]")
+    _contig("resid", resid), _contig("xw", xw), _contig("sumsq", sumsq), _contig("norm_weight", norm_weight)
+    f = _fn("gemm_skinny", "il_gemm_skinny_resid", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_float, _c_int, _c_int, _c_int,
+                                                    _c_void_p, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(bias), alpha, M, H, K, _ptr(resid), branch_scale, _ptr(norm_weight),
+             kind_of(norm_weight.dtype), _ptr(xw), _ptr(sumsq), _stream()), "gemm_skinny_resid")
+    return NormedInput(xw, sumsq, H, eps)
 
 
 def skinny_rope_ok(M: int, K: int, head_dim: int, rot_dim: int) -> bool:
@@ -414,7 +478,7 @@ def skinny_rope_ok(M: int, K: int, head_dim: int, rot_dim: int) -> bool:
 def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float, bias: Optional[torch.Tensor],
                      tok_pos: torch.Tensor, tok_entry: torch.Tensor, block_table: torch.Tensor, cache: Optional[torch.Tensor],
                      page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, rot_dim: int,
-                     inv_freq: Optional[torch.Tensor], mscale: float) -> None:
+                     inv_freq: Optional[torch.Tensor], mscale: float, norm_in: Optional[NormedInput] = None) -> None:
     """The q/k/v projection of up to 16 bfloat16 rows with what `rope_store` does in its epilogue: out[M, (heads + 2
     kv_heads) * head_dim] = alpha * x @ w^T (+ bias), q and k rotated, k and v written to their cache slots (if `cache`)."""
     _need_cuda(x, w, out, bias, tok_pos, tok_entry, block_table, cache, inv_freq)
@@ -437,10 +501,12 @@ def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha:
             raise KernelError("gemm_skinny_rope: cache bfloat16 [pages,2,kv_heads,page,head_dim]")
     f = _fn("gemm_skinny", "il_gemm_skinny_rope",
             [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p,
-             _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p])
+             _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_int,
+             _c_float, _c_void_p])
+    np_, nb, nw, ne = _norm_args(norm_in, M)
     _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), _ptr(bias), alpha, M, K, _ptr(tok_pos),
              _ptr(tok_entry), _ptr(block_table), block_table.shape[1], _ptr(cache), page_size, n_heads, n_kv_heads, head_dim,
-             rot_dim, _ptr(inv_freq), mscale, _stream()), "gemm_skinny_rope")
+             rot_dim, _ptr(inv_freq), mscale, np_, nb, nw, ne, _stream()), "gemm_skinny_rope")
 
 
 def skinny_ok(M: int, K: int) -> bool:

@@ -73,7 +73,14 @@ class Attention(Mixer):
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed("paged_kv", n_kv_heads=self.nkv, head_dim=self.hd, window=self.window)
 
-    def forward(self, x, ctx, cache):
+    def accepts_normed(self, T):
+        return (self.dtype == torch.bfloat16 and self.fuse_rope
+                and ops.skinny_rope_ok(T, self.hidden, self.hd, self.position.rot_dim))
+
+    def fuses_tail(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_resid_ok(T, self.nh * self.hd, self.hidden)
+
+    def forward(self, x, ctx, cache, tail=None):
         T = x.shape[0]
         pos = self.position
         qkv = ctx.ws.rows("qkv", T, self.n_qkv, self.dtype)
@@ -81,15 +88,20 @@ class Attention(Mixer):
         if (self.dtype == torch.bfloat16 and self.fuse_rope
                 and ops.skinny_rope_ok(T, self.hidden, self.hd, pos.rot_dim)):
             # a few rows (decode): the projection rotates q and k and writes k, v to the cache in its epilogue
-            ops.gemm_skinny_rope(x, self.qkv.weight, qkv, self.qkv.alpha, self.qkv.bias, ctx.tok_pos, ctx.tok_entry,
-                                 cache.block_table, store, cache.page_size, self.nh, self.nkv, self.hd, pos.rot_dim,
-                                 pos.inv_freq, pos.mscale)
+            normed = isinstance(x, ops.NormedInput)
+            ops.gemm_skinny_rope(x.xw if normed else x, self.qkv.weight, qkv, self.qkv.alpha, self.qkv.bias, ctx.tok_pos,
+                                 ctx.tok_entry, cache.block_table, store, cache.page_size, self.nh, self.nkv, self.hd,
+                                 pos.rot_dim, pos.inv_freq, pos.mscale, norm_in=x if normed else None)
         else:
             self.qkv(x, qkv)
             ops.rope_store(qkv, ctx.tok_pos, ctx.tok_entry, cache.block_table, store, cache.page_size,
                            self.nh, self.nkv, self.hd, pos.rot_dim, pos.inv_freq, pos.mscale)
         out = ctx.ws.rows("attn_out", T, self.nh * self.hd, self.dtype)
         self.attend(qkv, out, ctx, cache)
+        if tail is not None:                      # o_proj adds into the residual and prepares the next norm itself
+            return ops.gemm_skinny_resid(out, self.o_proj.weight, self.o_proj.alpha, self.o_proj.bias, tail.resid, tail.scale,
+                                         tail.norm.weight, tail.norm.eps, ctx.ws.rows("xw_mixer", T, self.hidden, self.dtype),
+                                         ctx.ws.rows("sumsq_mixer", T, (self.hidden + 15) // 16, torch.float32))
         return self.o_proj(out, ctx.ws.rows("branch", T, self.hidden, self.dtype))
 
     # The fast bfloat16 kernels take pages of 16 keys and at most 64 query heads per kv head; anything

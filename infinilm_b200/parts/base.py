@@ -39,7 +39,19 @@ class Part:
         return f"{self.prefix}.{local}" if self.prefix else local
 
 
+class ResidualTail:
+    """Handed to a branch (mixer or feed-forward) whose last matrix product can finish the branch itself: add
+    `scale` * result into `resid` (float32 [T,H], in place) and prepare `norm` of the sum for the next product, which
+    then gets an `ops.NormedInput` instead of normalised rows. Saves the add+norm kernel between two products."""
+    __slots__ = ("resid", "scale", "norm")
+
+    def __init__(self, resid: torch.Tensor, scale: float, norm: "Norm"):
+        self.resid, self.scale, self.norm = resid, float(scale), norm
+
+
 class Norm(Part):
+    fusable_rms = False                          # True: an RMSNorm with `.weight` and `.eps` that a ResidualTail may name
+
     def add_norm(self, resid: torch.Tensor, branch: Optional[torch.Tensor], branch_scale: float,
                  out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """resid (f32 [T,H]) += branch_scale * branch; out = norm(resid). With `rows`, only those
@@ -61,6 +73,14 @@ class Mixer(Part):
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 
+    # A part that can read an `ops.NormedInput` as `x`, or take a `tail=ResidualTail` in `forward` and return the
+    # `ops.NormedInput` of the next norm, says so here for a step of T rows; by default it can do neither.
+    def accepts_normed(self, T: int) -> bool:
+        return False
+
+    def fuses_tail(self, T: int) -> bool:
+        return False
+
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         """x [T,H] in the compute dtype -> y [T,H]. `cache` is this run entry's view of the cache
         (`PagedKVView`, `StateView` or None); `cache.writable` is False when the entry reads
@@ -71,6 +91,12 @@ class Mixer(Part):
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
+
+    def accepts_normed(self, T: int) -> bool:     # see Mixer
+        return False
+
+    def fuses_tail(self, T: int) -> bool:
+        return False
 
 
 class Arrangement:
@@ -84,8 +110,16 @@ class Arrangement:
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
 
     def run(self, resid: torch.Tensor, pending, ctx, cache):
-        """`pending` is (branch, scale) not yet added to `resid`, or None. Returns the new pending."""
+        """`pending` is (branch, scale) not yet added to `resid`, or None, or an `ops.NormedInput` (the add is done and
+        this block's first norm prepared; only given if `accepts_normed_input`). Returns the new pending. An arrangement
+        with `takes_next_norm` has one more argument, `next_norm=None`: the first norm of the block that runs next, if that
+        block accepts a normed input; it may then return an `ops.NormedInput` for it."""
         raise NotImplementedError
+
+    takes_next_norm = False                      # True: `run` has the `next_norm` argument and may use it
+
+    def accepts_normed_input(self, T: int) -> bool:
+        return False
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {

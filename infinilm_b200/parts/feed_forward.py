@@ -39,12 +39,26 @@ class SwiGLU(FeedForward):
         self.gate_up.set(w, b)
         self.down.set(t["down_proj.weight"], t.get("down_proj.bias"))
 
-    def forward(self, x, ctx):
+    def accepts_normed(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden)
+
+    def fuses_tail(self, T):
+        return self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden) and ops.skinny_resid_ok(T, self.inter, self.hidden)
+
+    def forward(self, x, ctx, tail=None):
         T = x.shape[0]
         if self.dtype == torch.bfloat16 and ops.skinny_ok(T, self.hidden):
             # decode: gate and up rows streamed together, SiLU(gate)*up in the epilogue
             act = ctx.ws.rows("ffn_act", T, self.inter, self.dtype)
-            ops.gemm_skinny(x, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=True)
+            if isinstance(x, ops.NormedInput):
+                ops.gemm_skinny(x.xw, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=True, norm_in=x)
+            else:
+                ops.gemm_skinny(x, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=True)
+            if tail is not None:                  # down adds into the residual and prepares the next norm itself
+                return ops.gemm_skinny_resid(act, self.down.weight, self.down.alpha, self.down.bias, tail.resid, tail.scale,
+                                             tail.norm.weight, tail.norm.eps,
+                                             ctx.ws.rows("xw_ffn", T, self.hidden, self.dtype),
+                                             ctx.ws.rows("sumsq_ffn", T, (self.hidden + 15) // 16, torch.float32))
             return self.down(act, ctx.ws.rows("branch", T, self.hidden, self.dtype))
         gu = self.gate_up(x, ctx.ws.rows("gate_up", T, 2 * self.inter, self.dtype))
         act = ctx.ws.rows("ffn_act", T, self.inter, self.dtype)

@@ -17,6 +17,7 @@ from .spec import WeightSpec
 
 class RMSNorm(Norm):
     """params: size, eps."""
+    fusable_rms = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)

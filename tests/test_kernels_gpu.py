@@ -188,6 +188,75 @@ def test_gemm_skinny_rope(cuda_device, nh, nkv, hd, rot, M):
     assert torch.equal(out2, out)
 
 
+@pytest.mark.parametrize("H,K", [(64, 96), (200, 72), (1000, 264), (4096, 512)])
+@pytest.mark.parametrize("M", [1, 7, 8, 12, 16])
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+def test_gemm_skinny_resid_and_normed_consumers(cuda_device, H, K, M, wdtype):
+    """The last product of a branch with the residual add in its epilogue, and the products that finish the norm:
+    against plain float32 formulas, and against the kernels they stand for (product, add_rmsnorm, product)."""
+    g = torch.Generator().manual_seed(31 + M)
+    x = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(H, K, generator=g) * 0.1).bfloat16()
+    bias = torch.randn(H, generator=g) if (M % 2) else None
+    resid0 = torch.randn(M, H, generator=g) * 2.0
+    nw = (1.0 + 0.3 * torch.randn(H, generator=g)).to(DT[wdtype])
+    alpha, bscale, eps = 0.6, 0.35, 3e-5
+    assert ops.skinny_resid_ok(M, K, H)
+    # plain formulas
+    y = (alpha * x.float() @ w.float().t() + (bias if bias is not None else 0.0)).bfloat16().float()
+    h_ref = resid0 + bscale * y
+    resid = resid0.clone().cuda()
+    xw = torch.full((M, H), float("nan"), device="cuda", dtype=torch.bfloat16)
+    nb = (H + 15) // 16
+    sumsq = torch.full((M, nb), float("nan"), device="cuda")
+    ni = ops.gemm_skinny_resid(x.cuda(), w.cuda(), alpha, bias.cuda() if bias is not None else None, resid, bscale, nw.cuda(), eps,
+                               xw, sumsq)
+    close(resid.cpu(), h_ref, "bfloat16", scale=y.abs().max() * bscale)   # one bfloat16 step of the branch at most
+    h = resid.cpu()
+    close(xw.float().cpu(), h * nw.float(), "bfloat16")
+    pad = torch.zeros(M, nb * 16)
+    pad[:, :H] = h * h
+    close(sumsq.cpu(), pad.view(M, nb, 16).sum(-1), "float32")
+    # against the kernels it stands for: the same residual bit for bit
+    branch = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_skinny(x.cuda(), w.cuda(), branch, alpha, bias.cuda() if bias is not None else None)
+    resid2 = resid0.clone().cuda()
+    normed = torch.empty(M, H, device="cuda", dtype=torch.bfloat16)
+    ops.add_rmsnorm(resid2, branch, bscale, nw.cuda(), eps, normed)
+    assert torch.equal(resid2, resid)
+    rstd = torch.rsqrt((h.double() ** 2).mean(-1, keepdim=True) + eps).float()
+    # consumer 1: gate and up with SiLU(gate) * up
+    N2 = 56
+    wgu = (torch.randn(2 * N2, H, generator=g) * (2.0 / H ** 0.5)).bfloat16()
+    act = torch.full((M, N2), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_skinny(ni.xw, wgu.cuda(), act, 1.0, None, glu=True, norm_in=ni)
+    gu = rstd * (xw.float().cpu() @ wgu.float().t())
+    close(act.float().cpu(), torch.nn.functional.silu(gu[:, :N2]) * gu[:, N2:], "bfloat16")
+    act2 = torch.empty_like(act)
+    ops.gemm_skinny(normed, wgu.cuda(), act2, 1.0, None, glu=True)
+    close(act.float().cpu(), act2.float().cpu(), "bfloat16")              # the norm rounded at another place
+    # consumer 2: q/k/v with rotation
+    nh, nkv, hd, page = 3, 1, 32, 16
+    Nq = (nh + 2 * nkv) * hd
+    wq = (torch.randn(Nq, H, generator=g) * (1.0 / H ** 0.5)).bfloat16()
+    starts = [5 * i + 1 for i in range(M)]
+    bt, cache = _paged_setup(M, [s + 1 for s in starts], nkv, hd, page, torch.bfloat16, 33)
+    tok_pos, tok_entry = torch.tensor(starts, dtype=torch.int32).cuda(), torch.arange(M, dtype=torch.int32).cuda()
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))).float().cuda()
+    outs = []
+    for src, nin in ((ni.xw, ni), (normed, None)):
+        o = torch.full((M, Nq), float("nan"), device="cuda", dtype=torch.bfloat16)
+        c = cache.clone().cuda()
+        ops.gemm_skinny_rope(src, wq.cuda(), o, 0.9, None, tok_pos, tok_entry, bt.cuda(), c, page, nh, nkv, hd, hd, inv_freq, 1.0,
+                             norm_in=nin)
+        outs.append((o.float().cpu(), c.float().cpu()))
+    close(outs[0][0], outs[1][0], "bfloat16")
+    close(outs[0][1], outs[1][1], "bfloat16")
+    assert torch.equal(outs[0][1] == 0, outs[1][1] == 0)
+    pre = 0.9 * rstd * (xw.float().cpu() @ wq.float().t())                 # before rotation: v is not rotated
+    close(outs[0][0][:, (nh + nkv) * hd:], pre[:, (nh + nkv) * hd:], "bfloat16")
+
+
 # -- attention -------------------------------------------------------------------------------------
 def _attn_reference(q, kc, bt, entry_of_tok, pos_of_tok, nh, nkv, hd, page, window):
     """q [T, nh, hd] f32; kc cache f32; returns [T, nh*hd]."""
