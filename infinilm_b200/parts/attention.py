@@ -126,8 +126,6 @@ class Attention(Mixer):
             base = n_dec * self.nkv * ((G + 15) // 16)
             # as many splits as fill one wave of blocks (two per SM), never more: a second, part-filled wave costs more
             n_splits = max(1, min(self.TARGET_BLOCKS // base, (max_pages + 3) // 4, 128))
-            if os.environ.get("IL_DBG_SPLITS"):
-                n_splits = int(os.environ["IL_DBG_SPLITS"])
             cluster_max = min(self.cluster_merge, ops.attention_decode_cluster_max(self.hd)) if self.cluster_merge else 0
             if cluster_max > 0:
                 # the splits of a request and kv head as one thread-block cluster that merges its own partial results:
