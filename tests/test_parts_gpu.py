@@ -177,3 +177,44 @@ def test_sharp_attention_far_keys(cuda_device, dtype):
         got = run_cut(eng, ids, cuts)
         bad = first_bad_row(got, ref, TOL[dtype])
         assert bad is None, f"cuts {cuts[:3]}..: first wrong position {bad}, rel err {rel_err(got, ref):.3e}"
+
+
+@pytest.mark.parametrize("name", ["c", "d"])
+@pytest.mark.parametrize("cuts", [[9, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1], [20, 3, 2, 5, 16, 1]])
+def test_block_with_and_without_the_norm_in_its_products(cuda_device, cuts, name):
+    """The arrangement's two ways through a step of few rows - add+norm as kernels of their own, or the product before
+    adding into the residual and the product after dividing by the rms - against the plain model, and the fused way
+    with as many launches fewer as there are norms between two parts that can. Portions of 17 rows and more take the
+    kernels either way. Configuration c rotates half of a head (its q/k/v product does not take the norm), d all of it."""
+    from infinilm_b200 import ops
+    from infinilm_b200.parts.blocks import PreNormResidual
+    from tiny_configs import TINY
+    raw = TINY[name]()
+    w = make_weights(raw, 5)
+    ids = random_ids(sum(cuts), raw["vocab_size"], 77)
+    ref = plain_logits(raw, w, ids, "bfloat16")
+    was = PreNormResidual.FUSE_NORM
+    got, launches = {}, {}
+    try:
+        for fuse in (False, True):
+            PreNormResidual.FUSE_NORM = fuse
+            eng = build_engine(raw, w, "bfloat16")
+            n0 = ops.launch_count()
+            got[fuse] = run_cut(eng, ids, cuts)
+            launches[fuse] = ops.launch_count() - n0
+        model, saved = eng.model, 0
+        for T in cuts:
+            for i, st in enumerate(model.order):
+                blk = model.blocks[st.layer]
+                nxt = model.blocks[model.order[i + 1].layer] if i + 1 < len(model.order) else None
+                saved += int(blk.mixer.fuses_tail(T) and blk.ffn.accepts_normed(T))
+                saved += int(nxt is not None and nxt.accepts_normed_input(T) and blk.ffn.fuses_tail(T))
+    finally:
+        PreNormResidual.FUSE_NORM = was
+    for fuse in (False, True):
+        bad = first_bad_row(got[fuse], ref, TOL["bfloat16"])
+        assert bad is None, f"fuse={fuse}: first wrong position {bad} (rel err {rel_err(got[fuse][bad], ref[bad]):.2e})"
+    small = sum(1 for c in cuts if c <= ops.SKINNY_MAX_ROWS)
+    L = raw["num_hidden_layers"]
+    assert saved == small * (L if name == "c" else 2 * L - 1)
+    assert launches[False] - launches[True] == saved
