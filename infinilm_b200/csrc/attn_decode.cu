@@ -589,7 +589,8 @@ IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const v
 // first the cache seen as rows of head_dim, for boxes of [16 rows x 64 columns] with the 128-byte swizzle; then a view
 // with the dimensions (64 columns, 16 slots, head_dim / 64 column blocks, kv heads, 2 * pages) whose box is one page
 // of one kv head, K and V: it lands in shared memory as the same 2 KB tiles, [K, V][column block][slot][64]. The second
-// is all zero if the driver does not take it. n_rows = pages * 2 * kv heads * 16. Returns 0, or IL_UNSUPPORTED.
+// is all zero if the driver does not take it; so is the third, for the prefill kernel (below). out_maps: 3 x 128 bytes.
+// n_rows = pages * 2 * kv heads * 16. Returns 0, or IL_UNSUPPORTED.
 IL_EXPORT int il_attn_decode_kv_map(void* out_maps, const void* cache, long long n_rows, int hd, int nkv) {
     if (!AD_TMA_OK || hd != HEAD_DIM || nkv <= 0 || ((uintptr_t)cache & 15)) return IL_UNSUPPORTED;
     typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -603,7 +604,7 @@ IL_EXPORT int il_attn_decode_kv_map(void* out_maps, const void* cache, long long
             return IL_UNSUPPORTED;
         enc = (encode_fn)p;
     }
-    CUtensorMap m[2];
+    CUtensorMap m[3];
     memset(m, 0, sizeof(m));
     {
         cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)n_rows};
@@ -626,6 +627,20 @@ IL_EXPORT int il_attn_decode_kv_map(void* out_maps, const void* cache, long long
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r == CUDA_SUCCESS) m[1] = t;          // else: stays zero, the kernel copies 2 KB boxes
+    }
+    {
+        // 16 slots of one kv head (K or V of a page) as tensor-core tiles: (64 columns, 8 slots, column blocks, 2 groups of
+        // 8 slots, 16-slot blocks). The box lands as [group][column block][8 slots][64]: 1 KB tiles of 8 rows, those of one
+        // column block head_dim / 64 KB apart - a uniform stride over the pages of a key tile, which a descriptor needs.
+        cuuint64_t dims[5] = {64, 8, (cuuint64_t)(hd / 64), 2, (cuuint64_t)(n_rows / AD_PAGE)};
+        cuuint64_t strides[4] = {(cuuint64_t)hd * 2, 128, (cuuint64_t)8 * hd * 2, (cuuint64_t)AD_PAGE * hd * 2};
+        cuuint32_t box[5] = {64, 8, (cuuint32_t)(hd / 64), 2, 1};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        CUtensorMap t;
+        CUresult r = enc(&t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS) m[2] = t;          // else: stays zero; the tensor-memory prefill kernel is then not used
     }
     memcpy(out_maps, m, sizeof(m));
     return IL_OK;

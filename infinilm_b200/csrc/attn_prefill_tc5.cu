@@ -6,20 +6,24 @@
 //   (row r -> token r / G, head r % G), and walks the keys in tiles of 64 (four pages of 16).
 //     S = Q.K^T   tcgen05.mma, M 128, N 64, both operands in shared memory (K-major, 128-byte swizzle): Q is put
 //                 there once by the softmax threads, K pages arrive as TMA tensor copies. S lives in tensor memory,
-//                 two buffers, so the product of tile j+1 runs while tile j is in the softmax.
+//                 two buffers; a buffer is free again as soon as the softmax threads have read it into registers, so
+//                 the scores of tile j+2 are computed under the softmax of tile j.
 //     softmax     four warps, one thread a row: tcgen05.ld of the row's 64 scores, mask where the tile touches the
 //                 row's causal or window edge, base-2 exponent with the scale folded in, f32 sum. The running
 //                 maximum is raised only when a tile's maximum is more than 2^8 above it; then the row of O is
-//                 rescaled in tensor memory. P goes back to tensor memory as bfloat16, over its own scores.
-//     O += P.V    tcgen05.mma, M 128, N head_dim, A = P from tensor memory, B = the V pages as they lie in the
+//                 rescaled in tensor memory. P goes to shared memory as bfloat16 (a K-major tile like Q's).
+//     O += P.V    tcgen05.mma, M 128, N head_dim, A = P from shared memory, B = the V pages as they lie in the
 //                 cache (keys by head_dim: MN-major); O accumulates in tensor memory and is divided by the row
 //                 sums at the end.
-//   Roles by warp: 0 producer (TMA; K and V each in a ring of two slots, K freed as soon as its scores are computed,
-//   V when its product is), 1 tensor-core issue and tensor-memory allocation, 2-5 softmax and output. 256 columns of
-//   tensor memory and about 98 KB of shared memory: two blocks per SM, one's products under the other's softmax.
-//   (Two softmax threads a row, each with half the columns, measured slower: 71 against 53 us at 2,048 tokens. So did one
-//   block per SM that owns two tiles of 128 rows, loads the keys once for both and issues the products of both in
-//   turn: 67 us - its two softmax groups run in step and meet at the exponential unit, where two blocks drift apart.)
+//   Roles by warp: 0 producer (TMA; one copy a page through a view of the cache whose box lands as tensor-core tiles;
+//   K and V each in a ring of two slots, K freed as soon as its scores are computed, V when its product is; page ids
+//   are read from the block table 32 at a time, ahead of their use), 1 tensor-memory allocation and issue of the
+//   score products, 2 issue of the output products, 3-6 softmax and output. 256 columns of tensor memory and 112 KB of shared memory: two blocks per SM.
+//   What was measured on the way (2,048 tokens, 32 heads on 2 kv heads, head_dim 128): P in tensor memory over its own
+//   scores held a score buffer until the product P.V had read it, and the softmax threads stood idle four clocks in
+//   ten waiting for the next scores; page ids read where they were needed and 2 KB copies (16 a tile) kept the producer
+//   busy 1,000 clocks a tile. Two softmax threads a row (71 against 53 us), one block per SM with two tiles of 128
+//   rows (67 us) and tiles of 128 keys with single-buffered scores (no gain) were slower or equal.
 //
 //   Pages past the entry's last page are read as the last page again (finite values the mask removes).
 //   Every mbarrier wait is bounded; one that runs out sets *status and all roles leave their loops.
@@ -39,20 +43,28 @@ constexpr int PT_ROWS = 128;
 constexpr int PT_KEYS = 64;
 constexpr int PT_PAGE = 16;
 constexpr int PT_TILE_PAGES = PT_KEYS / PT_PAGE;
-constexpr int PT_STAGES = 2;
+constexpr int PT_K_STAGES = 2, PT_V_STAGES = 2;
 constexpr int PT_Q_HALF = PT_ROWS * 128;          // bytes of one column block of Q
 constexpr int PT_Q_BYTES = PT_HALVES * PT_Q_HALF;
-constexpr int PT_K_HALF = PT_KEYS * 128;
-constexpr int PT_K_BYTES = PT_HALVES * PT_K_HALF; // K tile; the V tile has the same size
-constexpr int PT_STAGE_BYTES = 2 * PT_K_BYTES;
-constexpr int PT_THREADS = 192;
+constexpr int PT_P_BYTES = PT_ROWS * 128;         // P: 128 rows x 64 keys, bfloat16
+constexpr int PT_ATOM = PT_HALVES * 1024;         // K and V tiles: 1 KB atoms (8 keys x 64 columns); a column block's atoms this far apart,
+constexpr int PT_PAGE_BYTES = 2 * PT_ATOM;        // the next column block's 1 KB further; a page (16 keys) is two atoms of each
+constexpr int PT_K_BYTES = PT_TILE_PAGES * PT_PAGE_BYTES;   // K tile; the V tile has the same size
+constexpr int PT_THREADS = 224;
 constexpr int PT_TMEM_COLS = 256;
 constexpr int PT_COL_O = 2 * PT_KEYS;             // S buffers at columns 0 and 64, O behind them
-constexpr int PT_N_BARS = 1 + 4 * PT_STAGES + 2 + 2 + 1;
-constexpr int PT_SMEM = 1024 + PT_Q_BYTES + PT_STAGES * PT_STAGE_BYTES + PT_N_BARS * 8 + 16;
+constexpr int PT_N_BARS = 1 + 2 * PT_K_STAGES + 2 * PT_V_STAGES + 2 + 2 + 1 + 1;
+// no slack for aligning the base: two blocks of head_dim 128 fill an SM's shared memory to within 2 KB; the base is checked instead
+constexpr int PT_SMEM = PT_Q_BYTES + PT_P_BYTES + (PT_K_STAGES + PT_V_STAGES) * PT_K_BYTES + PT_N_BARS * 8 + 16;
 constexpr unsigned PT_SPIN = 1u << 22;
 constexpr float PT_RAISE = 8.f;                   // the running maximum follows a tile's only beyond this (log2 units)
 
+// K or V of one page of one kv head (16 keys, all of head_dim) in one copy: the box of the cache's third tensor map
+// (il_attn_decode_kv_map), which lands as [8 keys][column block][8 keys x 64 columns]: 1 KB atoms, interleaved by column block.
+__device__ __forceinline__ void pt_tma_page(uint32_t dst, const CUtensorMap* map, int block16, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %3, %3, %3, %4}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(block16) : "memory");
+}
 __device__ __forceinline__ float pt_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -68,8 +80,11 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
     __nv_bfloat16* __restrict__ out, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_qstart,
     const int* __restrict__ entry_kvlen, int first_entry, int n_entries, int nh, int nkv, float scale_log2, int window, int tpt,
     int* __restrict__ status) {
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char smem[];
+    if (t5_smem(smem) & 1023u) {                  // the swizzled tiles need 1 KB alignment; dynamic shared memory starts on it
+        if (threadIdx.x == 0) atomicExch(status, 30);
+        return;
+    }
     const int G = nh / nkv;
     const int g = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -95,28 +110,35 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
     const int n_tiles = (page_last - page_first) / PT_TILE_PAGES + 1;
 
     unsigned char* q_smem = smem;
-    unsigned char* kv_smem = smem + PT_Q_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_smem + PT_STAGES * PT_STAGE_BYTES);
+    unsigned char* p_smem = smem + PT_Q_BYTES;
+    unsigned char* k_smem = p_smem + PT_P_BYTES;
+    unsigned char* v_smem = k_smem + PT_K_STAGES * PT_K_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_smem + PT_V_STAGES * PT_K_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + PT_N_BARS);
     const uint32_t bar0 = t5_smem(bars);
     const uint32_t q_full = bar0;                                     // Q is in shared memory (128 arrivals)
-    const uint32_t k_full0 = bar0 + 8, v_full0 = k_full0 + 8 * PT_STAGES, k_empty0 = v_full0 + 8 * PT_STAGES;
-    const uint32_t v_empty0 = k_empty0 + 8 * PT_STAGES, s_full0 = v_empty0 + 8 * PT_STAGES;               // a tile's scores are complete (tcgen05.commit)
-    const uint32_t p_full0 = s_full0 + 16;                            // a tile's P is in tensor memory (4 warps)
-    const uint32_t o_done = p_full0 + 16;                             // a tile's P.V has been added to O (tcgen05.commit)
+    const uint32_t k_full0 = bar0 + 8, k_empty0 = k_full0 + 8 * PT_K_STAGES;
+    const uint32_t v_full0 = k_empty0 + 8 * PT_K_STAGES, v_empty0 = v_full0 + 8 * PT_V_STAGES;
+    const uint32_t s_full0 = v_empty0 + 8 * PT_V_STAGES;              // a tile's scores are complete (tcgen05.commit)
+    const uint32_t s_free0 = s_full0 + 16;                            // ... and read into registers: the buffer may be written again (4 warps)
+    const uint32_t p_full = s_free0 + 16;                             // a tile's P is in shared memory (4 warps)
+    const uint32_t o_done = p_full + 8;                               // a tile's P.V has been added to O, P may be written again (tcgen05.commit)
 
     if (threadIdx.x == 0) {
         t5_mbar_init(q_full, 128);
-        for (int s = 0; s < PT_STAGES; ++s) {
+        for (int s = 0; s < PT_K_STAGES; ++s) {
             t5_mbar_init(k_full0 + 8 * s, 1);
-            t5_mbar_init(v_full0 + 8 * s, 1);
             t5_mbar_init(k_empty0 + 8 * s, 1);
+        }
+        for (int s = 0; s < PT_V_STAGES; ++s) {
+            t5_mbar_init(v_full0 + 8 * s, 1);
             t5_mbar_init(v_empty0 + 8 * s, 1);
         }
         for (int b = 0; b < 2; ++b) {
             t5_mbar_init(s_full0 + 8 * b, 1);
-            t5_mbar_init(p_full0 + 8 * b, 4);
+            t5_mbar_init(s_free0 + 8 * b, 4);
         }
+        t5_mbar_init(p_full, 4);
         t5_mbar_init(o_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -128,16 +150,23 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------- producer: K and V pages by TMA, a ring of slots for each ----------------
-        // One K or V tile: lane 0 waits for the ring slot, then one lane per box of [16 keys x 64 columns]. The waits come
-        // in the order in which the tensor core frees the slots: K(j+1) after S(j-1), then V(j) after O+=P.V(j-2).
-        constexpr int NBOX = PT_TILE_PAGES * PT_HALVES;
+        // ---------------- producer: K and V pages by TMA ----------------
+        // One K or V tile: lane 0 waits for the slot, then one lane per page. Page ids come from the block table ahead of
+        // their use: lane l holds the id of page base + l (`cur`) and of page base + 32 + l (`nxt`, still in flight when
+        // it is loaded); a page's id is a shuffle away.
+        int base = page_first;
+        int cur = bt[min(base + lane, page_last)], nxt = bt[min(base + 32 + lane, page_last)];
         auto issue = [&](int j, int kv) -> bool {
-            const int stage = j % PT_STAGES;
+            const int stage = kv ? j % PT_V_STAGES : j % PT_K_STAGES, round = kv ? j / PT_V_STAGES : j / PT_K_STAGES;
             const uint32_t full = (kv ? v_full0 : k_full0) + 8 * stage;
+            while (kv && page_first + j * PT_TILE_PAGES >= base + 32) {   // V(j) is the tile furthest behind: the window follows it
+                base += 32;
+                cur = nxt;
+                nxt = bt[min(base + 32 + lane, page_last)];
+            }
             int ok = 1;
             if (lane == 0) {
-                if (!t5_mbar_wait((kv ? v_empty0 : k_empty0) + 8 * stage, ((uint32_t)(j / PT_STAGES) & 1u) ^ 1u, PT_SPIN)) {
+                if (!t5_mbar_wait((kv ? v_empty0 : k_empty0) + 8 * stage, ((uint32_t)round & 1u) ^ 1u, PT_SPIN)) {
                     atomicExch(status, 31);
                     ok = 0;
                 } else {
@@ -145,69 +174,76 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (ok && lane < NBOX) {
-                const int p = lane / PT_HALVES, kk = lane - p * PT_HALVES;
-                const int pidx = min(page_first + j * PT_TILE_PAGES + p, page_last);
-                const int page = bt[pidx];
-                const int row = ((page * 2 + kv) * nkv + g) * PT_PAGE;
-                const uint32_t dst = t5_smem(kv_smem + stage * PT_STAGE_BYTES + kv * PT_K_BYTES + kk * PT_K_HALF + p * (PT_PAGE * 128));
-                t5_tma_2d(dst, &kv_map, kk * 64, row, full);
+            const int p = lane % PT_TILE_PAGES;
+            const int off = min(page_first + j * PT_TILE_PAGES + p, page_last) - base;      // 0 .. 63: K runs ahead of V
+            const int id_cur = __shfl_sync(0xffffffffu, cur, off & 31), id_nxt = __shfl_sync(0xffffffffu, nxt, off & 31);
+            if (ok && lane < PT_TILE_PAGES) {
+                const int page = off < 32 ? id_cur : id_nxt;
+                const uint32_t dst = t5_smem((kv ? v_smem : k_smem) + stage * PT_K_BYTES + p * PT_PAGE_BYTES);
+                pt_tma_page(dst, &kv_map, (page * 2 + kv) * nkv + g, full);
             }
             return ok != 0;
         };
+        // K runs up to two tiles ahead (its slots are free once the scores are computed), V follows the products
         bool ok = issue(0, 0);
+        if (ok && n_tiles > 1) ok = issue(1, 0);
         for (int j = 0; j < n_tiles && ok; ++j) {
-            if (j + 1 < n_tiles) ok = issue(j + 1, 0);
-            if (ok) ok = issue(j, 1);
+            ok = issue(j, 1);
+            if (ok && j + 2 < n_tiles) ok = issue(j + 2, 0);
         }
     } else if (warp == 1) {
-        // ---------------- tensor-core issue: S(0), S(1), O+=P.V(0), S(2), O+=P.V(1), ... ----------------
+        // ---------------- tensor-core issue, scores: S(j) as soon as K(j) is there and the buffer has been read out ----------------
+        // Two issuing threads, one for each kind of product: a wait on an mbarrier costs the thread about 200 clocks
+        // even when it is over already, and one thread with four of them a tile was what a tile's time came to.
         if (lane == 0) {
             // The issuing thread must keep up with the tensor core (a product every 32 to 64 clocks), so every descriptor
             // is made here, once: per product only an add of a constant remains. In a descriptor the address field counts
-            // 16-byte units: 32 bytes along K inside the swizzle span are +2, the next 64 columns +half/16.
-            const uint32_t idesc_s = t5_idesc(PT_ROWS, PT_KEYS, false), idesc_o = t5_idesc(PT_ROWS, PT_HD, true);
+            // 16-byte units: 32 bytes along K inside the swizzle span are +2.
+            const uint32_t idesc_s = t5_idesc(PT_ROWS, PT_KEYS, false);
             const uint64_t q_desc = t5_desc(t5_smem(q_smem), 16, 1024);
-            const uint64_t k_desc0 = t5_desc(t5_smem(kv_smem), 16, 1024);                  // slot s: + s * slot bytes / 16
-            const uint64_t v_desc0 = t5_desc(t5_smem(kv_smem + PT_K_BYTES), PT_K_HALF, 1024);
-            const uint32_t o_tmem = tmem_base + PT_COL_O;
+            const uint64_t k_desc0 = t5_desc(t5_smem(k_smem), 16, PT_ATOM);                // slot s: + s * slot bytes / 16
             bool ok = t5_mbar_wait(q_full, 0, PT_SPIN);
             if (!ok) atomicExch(status, 32);
-            auto issue_pv = [&](int i) -> bool {
-                const int s = i % PT_STAGES, b = i & 1;
-                if (!t5_mbar_wait(v_full0 + 8 * s, (uint32_t)(i / PT_STAGES) & 1u, PT_SPIN)) { atomicExch(status, 34); return false; }
-                if (!t5_mbar_wait(p_full0 + 8 * b, (uint32_t)(i >> 1) & 1u, PT_SPIN)) { atomicExch(status, 33); return false; }
-                t5_fence_after();
-                const uint64_t vd = v_desc0 + (uint64_t)(s * (PT_STAGE_BYTES >> 4));
-                const uint32_t p_tmem = tmem_base + (uint32_t)(b * PT_KEYS);
-                t5_mma_ts(o_tmem, p_tmem, vd, idesc_o, i > 0 ? 1u : 0u);
-#pragma unroll
-                for (int kk = 1; kk < PT_KEYS / 16; ++kk)     // 16 keys a product: 8 columns of P, 2 KB of V
-                    t5_mma_ts(o_tmem, p_tmem + kk * 8, vd + (uint64_t)(kk * (2048 >> 4)), idesc_o, 1u);
-                t5_commit(v_empty0 + 8 * s);                  // the V slot is free once these products have read it
-                t5_commit(o_done);
-                return true;
-            };
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j % PT_STAGES, b = j & 1;
-                if (!t5_mbar_wait(k_full0 + 8 * s, (uint32_t)(j / PT_STAGES) & 1u, PT_SPIN)) { atomicExch(status, 35); ok = false; break; }
+                const int s = j % PT_K_STAGES, b = j & 1;
+                if (!t5_mbar_wait(k_full0 + 8 * s, (uint32_t)(j / PT_K_STAGES) & 1u, PT_SPIN)) { atomicExch(status, 35); ok = false; break; }
+                // the score buffer: read out by the softmax of tile j-2 (nothing to wait for on a buffer's first use)
+                if (j >= 2 && !t5_mbar_wait(s_free0 + 8 * b, (uint32_t)((j >> 1) - 1) & 1u, PT_SPIN)) { atomicExch(status, 39); ok = false; break; }
                 t5_fence_after();
-                const uint64_t kd = k_desc0 + (uint64_t)(s * (PT_STAGE_BYTES >> 4));
+                const uint64_t kd = k_desc0 + (uint64_t)(s * (PT_K_BYTES >> 4));
                 const uint32_t s_tmem = tmem_base + (uint32_t)(b * PT_KEYS);
 #pragma unroll
                 for (int kk = 0; kk < PT_HD / 16; ++kk) {
                     const uint64_t off_q = (uint64_t)((kk >> 2) * (PT_Q_HALF >> 4) + (kk & 3) * 2);
-                    const uint64_t off_k = (uint64_t)((kk >> 2) * (PT_K_HALF >> 4) + (kk & 3) * 2);
+                    const uint64_t off_k = (uint64_t)((kk >> 2) * (1024 >> 4) + (kk & 3) * 2);
                     t5_mma_ss(s_tmem, q_desc + off_q, kd + off_k, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 t5_commit(s_full0 + 8 * b);
                 t5_commit(k_empty0 + 8 * s);                  // and the K slot is free
-                if (j > 0) ok = issue_pv(j - 1);
             }
-            if (ok) issue_pv(n_tiles - 1);
+        }
+    } else if (warp == 2) {
+        // ---------------- tensor-core issue, outputs: O += P.V(j) as soon as P(j) and V(j) are there ----------------
+        if (lane == 0) {
+            const uint32_t idesc_o = t5_idesc(PT_ROWS, PT_HD, true);
+            const uint64_t p_desc = t5_desc(t5_smem(p_smem), 16, 1024);
+            const uint64_t v_desc0 = t5_desc(t5_smem(v_smem), 1024, PT_ATOM);
+            const uint32_t o_tmem = tmem_base + PT_COL_O;
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i % PT_V_STAGES;
+                if (!t5_mbar_wait(v_full0 + 8 * s, (uint32_t)(i / PT_V_STAGES) & 1u, PT_SPIN)) { atomicExch(status, 34); break; }
+                if (!t5_mbar_wait(p_full, (uint32_t)i & 1u, PT_SPIN)) { atomicExch(status, 33); break; }
+                t5_fence_after();
+                const uint64_t vd = v_desc0 + (uint64_t)(s * (PT_K_BYTES >> 4));
+#pragma unroll
+                for (int kk = 0; kk < PT_KEYS / 16; ++kk)     // 16 keys a product: 32 bytes along a row of P, one page of V
+                    t5_mma_ss(o_tmem, p_desc + (uint64_t)(kk * 2), vd + (uint64_t)(kk * (PT_PAGE_BYTES >> 4)), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                t5_commit(v_empty0 + 8 * s);                  // the V slot is free once these products have read it
+                t5_commit(o_done);                            // and so is P's place
+            }
         }
     } else {
-        // ---------------- softmax and output: warps 2..5 own tensor-memory lanes 32*(warp % 4) .. +31 ----------------
+        // ---------------- softmax and output: warps 3..6 own tensor-memory lanes 32*(warp % 4) .. +31 ----------------
         const int qd = warp & 3;
         const int r = qd * 32 + lane;                         // this thread's row
         const bool rvalid = r < rows_valid;
@@ -227,6 +263,7 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
             t5_mbar_arrive(q_full);
         }
         const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
+        unsigned char* p_row = p_smem + r * 128;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
@@ -237,6 +274,10 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
             t5_ld32(t_lane + b * PT_KEYS, sv);
             t5_ld32(t_lane + b * PT_KEYS + 32, sv + 32);
             t5_wait_ld();
+            // the scores are in registers: the tensor core may write this buffer again (tile j+2)
+            t5_fence_before();
+            __syncwarp();
+            if (lane == 0) t5_mbar_arrive(s_free0 + 8 * b);
             const int kb = (page_first + j * PT_TILE_PAGES) * PT_PAGE;
             if (kb + PT_KEYS - 1 > rpos || kb < rlo) {        // the tile touches this row's causal or window edge
 #pragma unroll
@@ -266,7 +307,7 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
             l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             m = m_new;
             if (j > 0) {
-                // O holds the tiles before this one only when their last product is through
+                // P's place in shared memory is free, and O holds the tiles before this one, only when their last product is through
                 if (!t5_mbar_wait(o_done, (uint32_t)(j - 1) & 1u, PT_SPIN)) { atomicExch(status, 37); ok = false; break; }
                 t5_fence_after();
                 if (__any_sync(0xffffffffu, raise)) {
@@ -279,13 +320,17 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
                         for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * corr);
                         t5_st32(t_lane + PT_COL_O + c0, ov);
                     }
+                    t5_wait_st();
                 }
             }
-            t5_st32(t_lane + b * PT_KEYS, sv);                // P over the first half of its own scores
-            t5_wait_st();
+            // P: this row's 64 values as 8 chunks of 16 bytes of the swizzled K-major tile
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = make_uint4(sv[4 * c], sv[4 * c + 1], sv[4 * c + 2], sv[4 * c + 3]);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             t5_fence_before();
             __syncwarp();
-            if (lane == 0) t5_mbar_arrive(p_full0 + 8 * b);
+            if (lane == 0) t5_mbar_arrive(p_full);
         }
         if (ok) {
             if (!t5_mbar_wait(o_done, (uint32_t)(n_tiles - 1) & 1u, PT_SPIN)) {
@@ -325,7 +370,7 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
 // Rows a block owns: it takes rows / (heads per kv head) consecutive tokens.
 IL_EXPORT int il_attn_prefill_tc5_rows() { return PT_ROWS; }
 
-// kv_map: the 128 bytes of the cache's tensor map (boxes of [16 rows x 64 columns], 128-byte swizzle), on the host.
+// kv_map: the 128 bytes of the cache's third tensor map (il_attn_decode_kv_map: a page's K or V as tensor-core tiles), on the host.
 // n_tiles_total: sum over entries [first_entry, n_entries) of ceil(q_len / tpt), tpt = max(1, rows / (nh/nkv)), rows = il_attn_prefill_tc5_rows().
 IL_EXPORT int il_attn_prefill_tc5(const void* qkv, int row_stride, void* out, const void* kv_map, const int* block_table,
                                   int bt_stride, const int* entry_qstart, const int* entry_kvlen, int page_size, int first_entry,

@@ -286,8 +286,8 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
         n_cnt = n_decode * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
         if not counters.is_cuda or counters.dtype != torch.int32 or counters.numel() < n_cnt:
             raise KernelError("attention_decode: counters must be int32 on the device, one per (row, kv head, head tile)")
-    if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != 256):
-        raise KernelError("attention_decode: kv_map must be the 256-byte host tensor kv_tensor_map returned")
+    if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != KV_MAP_BYTES):
+        raise KernelError("attention_decode: kv_map must be the host tensor kv_tensor_map returned")
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
@@ -311,9 +311,13 @@ def attention_decode_cluster_max(head_dim: int) -> int:
     return _cluster_max[head_dim]
 
 
+KV_MAP_BYTES = 384
+
+
 def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:
-    """The TMA tensor maps (2 x 128 bytes, on the host) of one layer's bfloat16 cache [pages,2,kv_heads,16,head_dim]: one
-    for boxes of [16 keys x 64 columns], one whose box is a whole page of a kv head (all zero if the driver refuses it).
+    """The TMA tensor maps (3 x 128 bytes, on the host) of one layer's bfloat16 cache [pages,2,kv_heads,16,head_dim]: one
+    for boxes of [16 keys x 64 columns], one whose box is a whole page of a kv head, one whose box is the K or V of a page
+    as tensor-core tiles (the last two all zero if the driver refuses them).
     None when the attention kernels have no tensor-copy path for this geometry (head_dim not a multiple of 64)."""
     if not cache.is_cuda or cache.dtype != torch.bfloat16 or cache.dim() != 5 or cache.shape[3] != 16 or cache.shape[4] % 64:
         return None
@@ -321,7 +325,7 @@ def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:
     lib = build.load("attn_decode", {"HEAD_DIM": hd})
     fn = lib.il_attn_decode_kv_map
     fn.argtypes, fn.restype = [_c_void_p, _c_void_p, ctypes.c_longlong, _c_int, _c_int], _c_int
-    m = torch.zeros(256, dtype=torch.uint8)
+    m = torch.zeros(KV_MAP_BYTES, dtype=torch.uint8)
     rc = fn(_c_void_p(m.data_ptr()), _ptr(cache), cache.numel() // hd, hd, cache.shape[2])
     return m if rc == 0 else None
 
@@ -359,9 +363,12 @@ def prefill_tc5_rows(head_dim: int) -> int:
     return _tc5_prefill_rows[head_dim]
 
 
-def prefill_tc5_ok(head_dim: int, group: int, page_size: int) -> bool:
-    """Whether the tensor-memory prefill kernel takes this geometry (the caller also needs the cache's tensor map)."""
-    return head_dim in (64, 128) and 0 < group <= 128 and page_size == 16
+def prefill_tc5_ok(head_dim: int, group: int, page_size: int, kv_map: Optional[torch.Tensor] = None) -> bool:
+    """Whether the tensor-memory prefill kernel takes this geometry and, if given, this tensor map of the cache (it
+    needs the third map of `kv_tensor_map`, a page's K or V as tensor-core tiles)."""
+    if not (head_dim in (64, 128) and 0 < group <= 128 and page_size == 16):
+        return False
+    return kv_map is None or (kv_map.numel() == KV_MAP_BYTES and bool(kv_map[256:].any()))
 
 
 def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Tensor, block_table: torch.Tensor,
@@ -373,13 +380,15 @@ def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Te
     _need_cuda(qkv, out, block_table, entry_qstart, entry_kvlen)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc5: bfloat16 tensors")
+    if kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != KV_MAP_BYTES or not bool(kv_map[256:].any()):
+        raise KernelError("attention_prefill_tc5: kv_map must be the host tensor kv_tensor_map returned, with its third map")
     if out.shape != (qkv.shape[0], n_heads * head_dim):
         raise KernelError("attention_prefill_tc5: out [T, heads*head_dim]")
     _contig("qkv", qkv), _contig("out", out), _contig("block_table", block_table)
     f = _fn("attn_prefill_tc5", "il_attn_prefill_tc5",
             [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
              _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
-    _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _c_void_p(kv_map.data_ptr()), _ptr(block_table), block_table.shape[1],
+    _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _c_void_p(kv_map.data_ptr() + 256), _ptr(block_table), block_table.shape[1],
              _ptr(entry_qstart), _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads,
              head_dim, scale, int(window or 0), _ptr(stream_status(qkv.device)), _stream()), "attention_prefill_tc5")
 
@@ -535,7 +544,7 @@ def check_status(device) -> None:
     code = int(t.item())
     if code:
         t.zero_()
-        raise KernelError(f"a kernel's bounded wait ran out (code {code}: 11-14 gemm_tc5, 21 attn_decode, 31-38 attn_prefill_tc5, "
+        raise KernelError(f"a kernel's bounded wait ran out (code {code}: 11-14 gemm_tc5, 21 attn_decode, 30-39 attn_prefill_tc5, "
                           f"others gemm_stream); the step's results are invalid")
 
 

@@ -146,7 +146,7 @@ class Attention(Mixer):
             # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128) and the cache
             # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.
             tc5 = (self.prefill_kernel != "mma" and cache.tma_map is not None
-                   and ops.prefill_tc5_ok(self.hd, G, cache.page_size))
+                   and ops.prefill_tc5_ok(self.hd, G, cache.page_size, cache.tma_map))
             tpt = max(1, (ops.prefill_tc5_rows(self.hd) if tc5 else 64) // G)
             n_tiles = sum((q + tpt - 1) // tpt for q in ctx.h_qlen[n_dec:])
             if tc5:
