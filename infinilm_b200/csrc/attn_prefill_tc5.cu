@@ -338,22 +338,36 @@ __global__ void __launch_bounds__(PT_THREADS, 2) attn_prefill_tc5_kernel(
             } else {
                 t5_fence_after();
                 const float inv = (l > 0.f) ? 1.f / l : 0.f;
-                __nv_bfloat16* orow = rvalid ? out + (size_t)(tok0 + tl) * nh * PT_HD + (size_t)(g * G + hh) * PT_HD : nullptr;
+                // The rows go out through shared memory (Q's place: every product that reads Q is through): a thread owns a
+                // row of tensor memory, but 16-byte stores 8 KB apart cost a block 2 us; a warp's 32 rows are stored
+                // 32 / CH at a time instead, CH lanes a row, each row's bytes contiguous.
+                constexpr int CH = PT_HD / 8;                 // 16-byte chunks of a row
+                unsigned char* stage = q_smem + qd * 32 * (PT_HD * 2);
 #pragma unroll
                 for (int c0 = 0; c0 < PT_HD; c0 += 32) {
                     uint32_t ov[32];
                     t5_ld32(t_lane + PT_COL_O + c0, ov);
                     t5_wait_ld();
-                    if (orow) {
 #pragma unroll
-                        for (int c = 0; c < 32; c += 8) {
-                            uint4 v;
-                            v.x = pt_pack(__uint_as_float(ov[c]) * inv, __uint_as_float(ov[c + 1]) * inv);
-                            v.y = pt_pack(__uint_as_float(ov[c + 2]) * inv, __uint_as_float(ov[c + 3]) * inv);
-                            v.z = pt_pack(__uint_as_float(ov[c + 4]) * inv, __uint_as_float(ov[c + 5]) * inv);
-                            v.w = pt_pack(__uint_as_float(ov[c + 6]) * inv, __uint_as_float(ov[c + 7]) * inv);
-                            *reinterpret_cast<uint4*>(orow + c0 + c) = v;
-                        }
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 v;
+                        v.x = pt_pack(__uint_as_float(ov[c]) * inv, __uint_as_float(ov[c + 1]) * inv);
+                        v.y = pt_pack(__uint_as_float(ov[c + 2]) * inv, __uint_as_float(ov[c + 3]) * inv);
+                        v.z = pt_pack(__uint_as_float(ov[c + 4]) * inv, __uint_as_float(ov[c + 5]) * inv);
+                        v.w = pt_pack(__uint_as_float(ov[c + 6]) * inv, __uint_as_float(ov[c + 7]) * inv);
+                        const int ch = (c0 + c) >> 3;
+                        *reinterpret_cast<uint4*>(stage + lane * (PT_HD * 2) + ((ch ^ (lane & 7)) << 4)) = v;
+                    }
+                }
+                __syncwarp();
+#pragma unroll
+                for (int it = 0; it < CH; ++it) {
+                    const int wr = it * (32 / CH) + lane / CH, ch = lane % CH;      // row of this warp, chunk of the row
+                    const int rr = qd * 32 + wr;
+                    if (rr < rows_valid) {
+                        const int t2 = rr / G, h2 = rr - t2 * G;
+                        const uint4 v = *reinterpret_cast<const uint4*>(stage + wr * (PT_HD * 2) + ((ch ^ (wr & 7)) << 4));
+                        *reinterpret_cast<uint4*>(out + (size_t)(tok0 + t2) * nh * PT_HD + (size_t)(g * G + h2) * PT_HD + ch * 8) = v;
                     }
                 }
             }
