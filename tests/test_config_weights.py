@@ -77,6 +77,17 @@ def test_bad_values():
         config_from_json(raw)
 
 
+def test_sizes_the_kernels_do_not_take_are_refused_when_the_model_is_built():
+    """A head size that is no multiple of 16 (or beyond 256) is refused by the mixer with the size named, before any
+    weight is read or any kernel runs."""
+    for hd in (40, 8, 272):
+        raw = tiny_a(); raw["head_dim"] = hd
+        with pytest.raises(ValueError, match=f"head_dim {hd}"):
+            CausalLM(describe_model(config_from_json(raw)), torch.bfloat16)
+    raw = tiny_a(); raw["head_dim"] = 48                                   # steps of 16 are taken
+    CausalLM(describe_model(config_from_json(raw)), torch.bfloat16)
+
+
 def test_registry_lookup_and_unknown():
     assert lookup_architecture({"architectures": ["MiniCPMForCausalLM"]}).config_cls is MiniCPM4Config
     assert lookup_architecture({"model_type": "minicpm4"}).config_cls is MiniCPM4Config
