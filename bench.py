@@ -119,7 +119,7 @@ def profile_step(args) -> int:
     from infinilm_b200.config import config_from_json
     from infinilm_b200.engine import Engine, StepEntry
     from infinilm_b200.weights import random_tensors
-    raw = dict(CONFIG_8B)
+    raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)
     raw["num_hidden_layers"] = args.layers or 2
     cfg = config_from_json(raw)
     B, P = args.batch, args.prompt_len
@@ -227,6 +227,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--sizes", choices=["8b", "0.5b"], default="8b",
+                    help="layer sizes: MiniCPM4-8B (the benchmark's) or MiniCPM4-0.5B (hidden 1024, head_dim 64; not the headline)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="tokens cached per request before decoding (a multiple of 2,048; default: the configuration's 2,048). "
                          "With more, prompts go in portions of 2,048 and `prefill` times the LAST portion, over the cache of the others")
@@ -265,7 +267,7 @@ def main() -> int:
         return profile_step(args)
     if args.workload != "default":
         return run_workload(args)
-    raw = dict(CONFIG_8B)
+    raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)
     full_layers = raw["num_hidden_layers"]
     n_layers = args.layers or full_layers
     raw["num_hidden_layers"] = n_layers
@@ -395,7 +397,7 @@ def main() -> int:
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights and uniform-random token ids",
-        "config": {"model": "MiniCPM4-8B sizes", "layers": n_layers, "layers_of_config": full_layers,
+        "config": {"model": "MiniCPM4-0.5B sizes" if args.sizes == "0.5b" else "MiniCPM4-8B sizes", "layers": n_layers, "layers_of_config": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "prompt_len": P, "context": max(CONTEXT, P + 2 * (K + W) + 8),

@@ -17,6 +17,8 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 from ..parts.spec import CacheNeed
 
 
@@ -92,6 +94,59 @@ class CacheGroup:
     pool: Optional[PagePool] = None               # paged_kv groups
     storage: Dict[int, object] = field(default_factory=dict)   # run-order index -> device tensor
     tma_maps: Dict[int, object] = field(default_factory=dict)  # run-order index -> tensor map of its storage (or absent)
+
+
+class PageTable(list):
+    """A request's page ids of one group (a list: -1 where a page was given back) with an int32 array kept beside it, so
+    that a step can copy the table into its descriptors without walking it: with hundreds of live requests, lists turned
+    into arrays every step were most of a decode step's host time. `append`, `tbl[i] = p` and `clear` keep the array in
+    step; any other change marks it stale and `array()` rebuilds it."""
+
+    def __init__(self, *a):
+        super().__init__(*a)
+        self._arr = np.empty(max(16, 2 * len(self)), dtype=np.int32)
+        self._arr[:len(self)] = self
+        self._stale = False
+
+    def append(self, p) -> None:
+        n = len(self)
+        super().append(p)
+        if n >= self._arr.shape[0]:
+            grown = np.empty(2 * self._arr.shape[0], dtype=np.int32)
+            grown[:n] = self._arr[:n]
+            self._arr = grown
+        self._arr[n] = p
+
+    def __setitem__(self, i, p) -> None:
+        super().__setitem__(i, p)
+        if isinstance(i, int):
+            self._arr[i] = p
+        else:
+            self._stale = True
+
+    def clear(self) -> None:
+        super().clear()
+        self._stale = False
+
+    def _touched(name):                           # noqa: N805 (a helper of the class body, deleted below)
+        def f(self, *a, **k):
+            self._stale = True
+            return getattr(list, name)(self, *a, **k)
+        return f
+    extend, insert, pop, remove = _touched("extend"), _touched("insert"), _touched("pop"), _touched("remove")
+    reverse, sort = _touched("reverse"), _touched("sort")
+    __delitem__, __iadd__, __imul__ = _touched("__delitem__"), _touched("__iadd__"), _touched("__imul__")
+    del _touched
+
+    def array(self) -> np.ndarray:
+        """The ids as int32 [len]; a view, valid until the table changes."""
+        n = len(self)
+        if self._stale:
+            if n > self._arr.shape[0]:
+                self._arr = np.empty(2 * n, dtype=np.int32)
+            self._arr[:n] = self
+            self._stale = False
+        return self._arr[:n]
 
 
 @dataclass
@@ -174,7 +229,7 @@ class CacheManager:
         seq = SequenceCache(seq_id, state_slot=self.slots.alloc())
         for g, grp in enumerate(self.groups):
             if grp.need.kind == "paged_kv":
-                seq.tables[g] = []
+                seq.tables[g] = PageTable()
         self.live[seq_id] = seq
         return seq
 
@@ -196,9 +251,12 @@ class CacheManager:
     def can_reserve(self, wants: Sequence[Tuple[SequenceCache, int]]) -> bool:
         """Whether all of `wants` (request, new length) can be reserved together now."""
         total: Dict[int, int] = {}
+        ps = self.page_size
         for seq, new_len in wants:
-            for g, n in self.pages_needed(seq, new_len).items():
-                total[g] = total.get(g, 0) + n
+            n_idx = (new_len + ps - 1) // ps
+            for g, tbl in seq.tables.items():
+                if n_idx > len(tbl):              # most decode steps need no page: nothing is built for them
+                    total[g] = total.get(g, 0) + n_idx - len(tbl)
         return all(self.groups[g].pool.n_free >= n for g, n in total.items())
 
     def reserve(self, seq: SequenceCache, new_len: int) -> None:
@@ -206,6 +264,9 @@ class CacheManager:
         self._check_open(seq)
         if new_len < seq.length:
             raise CacheStateError("a reservation cannot shrink a request")
+        n_idx = (new_len + self.page_size - 1) // self.page_size
+        if all(n_idx <= len(tbl) for tbl in seq.tables.values()):
+            return
         need = self.pages_needed(seq, new_len)
         for g, n in need.items():
             if self.groups[g].pool.n_free < n:
@@ -223,6 +284,8 @@ class CacheManager:
         seq.fresh_state = False
         for g, tbl in seq.tables.items():
             grp = self.groups[g]
+            if grp.need.window is None:
+                continue
             first = self._first_needed_page(grp, new_len)
             for idx in range(min(first, len(tbl))):
                 if tbl[idx] >= 0:

@@ -152,7 +152,8 @@ class StepRunner:
             for w in e.want:
                 if not 0 <= w < n:
                     raise StepError(f"entry {i} ({e.seq.seq_id!r}): wanted place {w} is outside its {n} tokens")
-            if max(e.tokens) >= vocab or (min(e.tokens) < 0 and device_tokens is None):
+            hi, lo = (e.tokens[0], e.tokens[0]) if n == 1 else (max(e.tokens), min(e.tokens))
+            if hi >= vocab or (lo < 0 and device_tokens is None):
                 raise StepError(f"request {e.seq.seq_id!r}: token id outside [0, {vocab})")
             if max_pos is not None and e.seq.length + n > max_pos:
                 raise StepError(f"request {e.seq.seq_id!r} would pass max_position_embeddings {max_pos}")
@@ -229,24 +230,45 @@ class StepRunner:
         s_bt = {g: take(Ep * widths[g]) for g in paged}
         s_prow, s_psrc = take(n_patch), take(n_patch)
         h_qlen, h_kvlen = [], []
-        for k, i in enumerate(order):
-            e = entries[i]
-            n, start = len(e.tokens), e.seq.length
-            a, b = qstart[k], qstart[k + 1]
-            h[s_tok[0] + a: s_tok[0] + b] = np.maximum(np.asarray(e.tokens, dtype=np.int64), 0)
-            h[s_pos[0] + a: s_pos[0] + b] = np.arange(start, start + n, dtype=np.int32)
-            h[s_ent[0] + a: s_ent[0] + b] = k
-            h[s_kv[0] + k] = start + n
-            h[s_rs[0] + k] = 0 if e.seq.fresh_state else e.seq.state_slot
-            h[s_wsl[0] + k] = e.seq.state_slot
-            h_qlen.append(n)
-            h_kvlen.append(start + n)
+        bt2d = {g: h[s_bt[g][0]: s_bt[g][1]].reshape(Ep, widths[g]) for g in paged}
+        for g in paged:
+            bt2d[g][:E].fill(-1)
+        if n_decode == E:
+            # every entry brings one token (the steps a serving run is mostly made of): whole columns at once, nothing
+            # per entry but its block table, copied from the array the cache keeps beside it
+            ordered = [entries[i] for i in order]
+            lens = np.fromiter((e.seq.length for e in ordered), dtype=np.int32, count=E)
+            h[s_tok[0]: s_tok[0] + E] = np.maximum(np.fromiter((e.tokens[0] for e in ordered), dtype=np.int64, count=E), 0)
+            h[s_pos[0]: s_pos[0] + E] = lens
+            h[s_ent[0]: s_ent[0] + E] = np.arange(E, dtype=np.int32)
+            h[s_kv[0]: s_kv[0] + E] = lens + 1
+            slots = np.fromiter((e.seq.state_slot for e in ordered), dtype=np.int32, count=E)
+            h[s_wsl[0]: s_wsl[0] + E] = slots
+            fresh = np.fromiter((e.seq.fresh_state for e in ordered), dtype=bool, count=E)
+            h[s_rs[0]: s_rs[0] + E] = np.where(fresh, 0, slots)
+            h_qlen = [1] * E
+            h_kvlen = (lens + 1).tolist()
             for g in paged:
-                w = widths[g]
-                tbl = e.seq.tables[g]
-                row = h[s_bt[g][0] + k * w: s_bt[g][0] + (k + 1) * w]
-                row[:len(tbl)] = tbl
-                row[len(tbl):] = -1
+                rows2d = bt2d[g]
+                for k, e in enumerate(ordered):
+                    tbl = e.seq.tables[g]
+                    rows2d[k, :len(tbl)] = tbl.array() if hasattr(tbl, "array") else tbl
+        else:
+            for k, i in enumerate(order):
+                e = entries[i]
+                n, start = len(e.tokens), e.seq.length
+                a, b = qstart[k], qstart[k + 1]
+                h[s_tok[0] + a: s_tok[0] + b] = np.maximum(np.asarray(e.tokens, dtype=np.int64), 0)
+                h[s_pos[0] + a: s_pos[0] + b] = np.arange(start, start + n, dtype=np.int32)
+                h[s_ent[0] + a: s_ent[0] + b] = k
+                h[s_kv[0] + k] = start + n
+                h[s_rs[0] + k] = 0 if e.seq.fresh_state else e.seq.state_slot
+                h[s_wsl[0] + k] = e.seq.state_slot
+                h_qlen.append(n)
+                h_kvlen.append(start + n)
+                for g in paged:
+                    tbl = e.seq.tables[g]
+                    bt2d[g][k, :len(tbl)] = tbl.array() if hasattr(tbl, "array") else tbl
         for k in range(E, Ep):                    # padding rows: one token at position 0 of the scratch page
             a = qstart[k]
             h[s_tok[0] + a] = 0

@@ -139,3 +139,32 @@ def test_random_orders_lose_nothing(seed):
     m.check_invariants()
     assert all(f == 24 for f in m.free_pages().values())
     assert m.slots.n_free == 5
+
+
+def test_page_table_array_follows_the_list():
+    """The int32 array a step copies from stays equal to the list under every way the list can change."""
+    import random
+
+    import numpy as np
+
+    from infinilm_b200.cache.manager import PageTable
+    rng = random.Random(5)
+    t = PageTable()
+    for step in range(400):
+        op = rng.choice(["append"] * 6 + ["set", "set", "clear", "extend", "pop", "slice", "iadd"])
+        if op == "append":
+            t.append(rng.randrange(1000))
+        elif op == "set" and len(t):
+            t[rng.randrange(len(t))] = -1
+        elif op == "clear" and rng.random() < 0.2:
+            t.clear()
+        elif op == "extend":
+            t.extend([7, 8, 9])
+        elif op == "pop" and len(t):
+            t.pop()
+        elif op == "slice" and len(t) > 2:
+            t[0:2] = [-1, -1]
+        elif op == "iadd":
+            t += [4]
+        a = t.array()
+        assert a.dtype == np.int32 and a.tolist() == list(t)
