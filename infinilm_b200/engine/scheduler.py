@@ -225,15 +225,27 @@ class Scheduler:
             return need if need <= free else -1
 
         # 1. running requests, decoding ones first (one token each), then unfinished prompts, oldest first
-        decoding = [r for r in self.running if not r.closing and r.n_tokens - r.n_cached == 1]
-        filling = [r for r in self.running if not r.closing and r.n_tokens - r.n_cached > 1]
-        for r in sorted(decoding, key=lambda r: r.arrival) + sorted(filling, key=lambda r: r.arrival):
+        # (lengths are taken once per request: with hundreds of live requests this pass is the scheduler's cost)
+        decoding, filling = [], []
+        for r in self.running:
+            if r.closing:
+                continue
+            left = len(r.prompt_token_ids) + len(r.output_token_ids) - r.seq.length
+            (decoding if left == 1 else filling).append(r)
+        decoding.sort(key=lambda r: r.arrival)
+        filling.sort(key=lambda r: r.arrival)
+        ps = self.cache.page_size
+        for r in decoding + filling:
             if out.preempted and any(r is v for v in out.preempted):      # preempted a moment ago
                 continue
             if budget <= 0:
                 break
-            toks = self._next_tokens(r, budget)
-            need = fits(r, len(toks))
+            if r.output_token_ids and len(r.prompt_token_ids) + len(r.output_token_ids) - r.seq.length == 1:
+                toks = r.output_token_ids[-1:]    # decoding: its last token, and a page only at a page's edge
+                need = fits(r, 1) if r.seq.length % ps == 0 or len(r.seq.tables) != 1 else 0
+            else:
+                toks = self._next_tokens(r, budget)
+                need = fits(r, len(toks))
             while need < 0:
                 if self.admission == "optimistic" and self._preempt_youngest(out, r):
                     free = self._free_pages() - sum(
@@ -246,7 +258,7 @@ class Scheduler:
                 continue                           # waits for pages; an older request will free some
             free -= need
             budget -= len(toks)
-            out.entries.append(ScheduledEntry(r, toks, samples=(r.n_cached + len(toks) == r.n_tokens)))
+            out.entries.append(ScheduledEntry(r, toks, samples=(r.seq.length + len(toks) == len(r.prompt_token_ids) + len(r.output_token_ids))))
 
         # 2. admissions, in arrival order; the first that does not fit stops the scan
         promised = None                           # pages the running requests may still ask for (worst case), summed once
