@@ -200,7 +200,9 @@ class Scheduler:
         """Gives back the pages of the youngest running request other than `keep` that is not
         already in this step. Returns False if there is none."""
         in_step = {id(e.request) for e in out.entries}
-        cands = [r for r in self.running if r is not keep and id(r) not in in_step]
+        # a request whose last token is on its way (`closing`) gives its pages back at the next retire anyway; taken
+        # out now it would be admitted and run a second time
+        cands = [r for r in self.running if r is not keep and id(r) not in in_step and not r.closing]
         if not cands:
             return False
         victim = max(cands, key=lambda r: r.arrival)
@@ -264,6 +266,9 @@ class Scheduler:
         promised = None                           # pages the running requests may still ask for (worst case), summed once
         while self.waiting and budget > 0 and len(self.running) < self.max_batch_size:
             r = self.waiting[0]
+            if r.finished:                        # ended (or was aborted) while it waited
+                self.waiting.popleft()
+                continue
             toks = self._next_tokens(r, budget)
             need = self._pages(len(toks))
             if self.admission == "worst_case":
@@ -293,6 +298,8 @@ class Scheduler:
         r.finish_reason = reason
         if r in self.running:
             self.running.remove(r)
+        if r in self.waiting:                     # preempted while its last token was on its way: nothing to recompute
+            self.waiting.remove(r)
         if r.seq is not None:
             self.cache.close(r.seq)
             r.seq = None

@@ -227,18 +227,42 @@ def test_pipelined_steps_run_one_token_ahead_and_drop_it_after_eos():
     assert cache.free_pages() == {0: 32} and not s.has_work()
 
 
-@pytest.mark.parametrize("seed", range(3))
-def test_pipelined_random_traffic(seed):
-    rng = random.Random(seed)
-    cache, s = make(num_pages=24, admission="optimistic", max_num_batched_tokens=40, chunk_size=16, max_batch_size=4)
-    reqs = [req(i, rng.randint(1, 60), max_tokens=rng.randint(1, 30)) for i in range(12)]
-    for r in reqs:
-        s.add_request(r)
-    run_pipelined(cache, s, lambda r: rng.choice([0, 5, 5, 5, 5, 5, 5, 5, 5]), max_steps=4000)
-    assert all(r.finished for r in reqs) and all(-1 not in r.output_token_ids for r in reqs)
-    for r in reqs:
-        if r.finish_reason is FinishReason.EOS_TOKEN:
-            assert r.output_token_ids[-1] == 0 and 0 not in r.output_token_ids[:-1]
-        else:
-            assert len(r.output_token_ids) == r.params.max_tokens and 0 not in r.output_token_ids[:-1]
-    assert cache.free_pages() == {0: 24} and not cache.live
+@pytest.mark.parametrize("pages", [8, 12, 24])
+@pytest.mark.parametrize("seed_block", range(4))
+def test_pipelined_random_traffic(seed_block, pages):
+    """Optimistic admission with so few pages that running requests are preempted while their last token is still on
+    its way: nothing is generated twice, nothing runs past its limits, nothing is left behind."""
+    for seed in range(100 * seed_block, 100 * seed_block + 100):
+        rng = random.Random(seed)
+        cache, s = make(num_pages=pages, admission="optimistic", max_num_batched_tokens=40, chunk_size=16, max_batch_size=4)
+        reqs = []
+        for i in range(12):
+            n_prompt, max_tokens = rng.randint(1, 60), rng.randint(1, 30)
+            while (n_prompt + max_tokens + 15) // 16 > pages:
+                n_prompt, max_tokens = rng.randint(1, 60), rng.randint(1, 30)
+            reqs.append(req(i, n_prompt, max_tokens=max_tokens))
+        for r in reqs:
+            s.add_request(r)
+        run_pipelined(cache, s, lambda r: rng.choice([0, 5, 5, 5, 5, 5, 5, 5, 5]), max_steps=4000)
+        assert not s.has_work(), seed
+        assert all(r.finished for r in reqs) and all(-1 not in r.output_token_ids for r in reqs), seed
+        for r in reqs:
+            assert len(r.output_token_ids) <= r.params.max_tokens, seed
+            if r.finish_reason is FinishReason.EOS_TOKEN:
+                assert r.output_token_ids[-1] == 0 and 0 not in r.output_token_ids[:-1], seed
+            else:
+                assert len(r.output_token_ids) == r.params.max_tokens and 0 not in r.output_token_ids[:-1], seed
+        assert cache.free_pages() == {0: pages} and not cache.live, seed
+
+
+def test_a_request_preempted_with_its_last_token_on_the_way_is_not_run_again():
+    # step 2: a needs its second page, the pool is empty, and b (younger) only waits for its last token to be read
+    cache, s = make(num_pages=2, admission="optimistic", chunk_size=16, max_batch_size=2)
+    a, b = req(0, 15, max_tokens=10), req(1, 14, max_tokens=2)
+    s.add_request(a), s.add_request(b)
+    steps = run_pipelined(cache, s, lambda r: 5)
+    assert b.output_token_ids == [5, 5] and b.finish_reason is FinishReason.LENGTH
+    assert len(a.output_token_ids) == 10 and not s.has_work() and cache.free_pages() == {0: 2}
+    assert s.n_preemptions == 0
+    # b brought its prompt once and one token after it; it was never admitted a second time
+    assert sum(1 for o in steps for e in o.entries if e.request is b) == 2
