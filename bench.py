@@ -271,8 +271,10 @@ def main() -> int:
     full_layers = raw["num_hidden_layers"]
     n_layers = args.layers or full_layers
     raw["num_hidden_layers"] = n_layers
+    # the branch scale is scale_depth / sqrt(layers): with fewer layers than the configuration has, scale_depth is
+    # lowered so that each branch keeps the scale it has in the full model
+    raw["scale_depth"] = raw["scale_depth"] * (n_layers / full_layers) ** 0.5
     cfg = config_from_json(raw)
-    # the branch scale follows the configured depth; keep the 32-layer value when fewer layers run
     hbm_peak, tf_peak, peak_src = load_peaks()
     dev = "cuda:0"
     torch.cuda.set_device(0)

@@ -99,28 +99,39 @@ class CacheGroup:
 class PageTable(list):
     """A request's page ids of one group (a list: -1 where a page was given back) with an int32 array kept beside it, so
     that a step can copy the table into its descriptors without walking it: with hundreds of live requests, lists turned
-    into arrays every step were most of a decode step's host time. `append`, `tbl[i] = p` and `clear` keep the array in
-    step; any other change marks it stale and `array()` rebuilds it."""
+    into arrays every step were most of a decode step's host time. The array is what the kernels read: a page of the
+    manager is `sub` kernel pages that lie one behind the other, so page p stands there as p*sub .. p*sub+sub-1.
+    `append`, `tbl[i] = p` and `clear` keep the array in step; any other change marks it stale and `array()` rebuilds it."""
 
-    def __init__(self, *a):
+    def __init__(self, *a, sub: int = 1):
         super().__init__(*a)
-        self._arr = np.empty(max(16, 2 * len(self)), dtype=np.int32)
-        self._arr[:len(self)] = self
-        self._stale = False
+        self.sub = int(sub)
+        self._arr = np.empty(max(16, 2 * len(self)) * self.sub, dtype=np.int32)
+        self._stale = len(self) > 0
+        self._steps = np.arange(self.sub, dtype=np.int32)
+
+    def _put(self, i: int, p: int) -> None:
+        sub = self.sub
+        if sub == 1:
+            self._arr[i] = p
+        elif p < 0:
+            self._arr[i * sub: (i + 1) * sub] = -1
+        else:
+            self._arr[i * sub: (i + 1) * sub] = p * sub + self._steps
 
     def append(self, p) -> None:
         n = len(self)
         super().append(p)
-        if n >= self._arr.shape[0]:
+        if (n + 1) * self.sub > self._arr.shape[0]:
             grown = np.empty(2 * self._arr.shape[0], dtype=np.int32)
-            grown[:n] = self._arr[:n]
+            grown[:n * self.sub] = self._arr[:n * self.sub]
             self._arr = grown
-        self._arr[n] = p
+        self._put(n, p)
 
     def __setitem__(self, i, p) -> None:
         super().__setitem__(i, p)
         if isinstance(i, int):
-            self._arr[i] = p
+            self._put(i if i >= 0 else len(self) + i, p)
         else:
             self._stale = True
 
@@ -139,14 +150,15 @@ class PageTable(list):
     del _touched
 
     def array(self) -> np.ndarray:
-        """The ids as int32 [len]; a view, valid until the table changes."""
+        """The kernel page ids as int32 [len * sub]; a view, valid until the table changes."""
         n = len(self)
         if self._stale:
-            if n > self._arr.shape[0]:
-                self._arr = np.empty(2 * n, dtype=np.int32)
-            self._arr[:n] = self
+            if n * self.sub > self._arr.shape[0]:
+                self._arr = np.empty(2 * n * self.sub, dtype=np.int32)
+            for i, p in enumerate(self):
+                self._put(i, p)
             self._stale = False
-        return self._arr[:n]
+        return self._arr[:n * self.sub]
 
 
 @dataclass
@@ -161,6 +173,8 @@ class SequenceCache:
 
 
 class CacheManager:
+    KERNEL_PAGE = 16
+
     def __init__(self, needs: Sequence[Optional[CacheNeed]], page_size: int, num_pages: int, max_seqs: int,
                  device=None, dtype=None, pages_per_group: Optional[Dict[int, int]] = None):
         """`needs[i]` is what run-order entry i keeps (None: nothing). `num_pages` pages are made
@@ -168,6 +182,11 @@ class CacheManager:
         self.page_size, self.max_seqs = int(page_size), int(max_seqs)
         if self.page_size <= 0 or (self.page_size & (self.page_size - 1)):
             raise ValueError("page_size must be a power of two")
+        # What the kernels call a page is `KERNEL_PAGE` tokens (the tile of the attention kernels). A larger page of the
+        # manager is `sub` of them one behind the other in memory: requests get and give back whole pages, block tables
+        # name kernel pages. A smaller page is a kernel page of its own size (plain kernels only).
+        self.kernel_page = min(self.page_size, self.KERNEL_PAGE)
+        self.sub = self.page_size // self.kernel_page
         self.groups: List[CacheGroup] = []
         self.group_of_entry: Dict[int, int] = {}
         by_key: Dict[Tuple, int] = {}
@@ -201,13 +220,13 @@ class CacheManager:
             for i in grp.entries:
                 if n.kind == "paged_kv":
                     # one page more than the pool hands out: padding rows of a replayed step write there
-                    shape = (grp.pool.n_pages + 1, 2, n.n_kv_heads, self.page_size, n.head_dim)
+                    shape = ((grp.pool.n_pages + 1) * self.sub, 2, n.n_kv_heads, self.kernel_page, n.head_dim)
                     dt = self.dtype
                 else:
                     shape = (self.slots.n_slots,) + tuple(n.shape)
                     dt = torch.float32 if n.dtype == "float32" else self.dtype
                 grp.storage[i] = torch.zeros(shape, dtype=dt, device=self.device)
-                if n.kind == "paged_kv" and dt == torch.bfloat16 and self.page_size == 16:
+                if n.kind == "paged_kv" and dt == torch.bfloat16 and self.kernel_page == 16:
                     from .. import ops
                     m = ops.kv_tensor_map(grp.storage[i])
                     if m is not None:
@@ -229,7 +248,7 @@ class CacheManager:
         seq = SequenceCache(seq_id, state_slot=self.slots.alloc())
         for g, grp in enumerate(self.groups):
             if grp.need.kind == "paged_kv":
-                seq.tables[g] = PageTable()
+                seq.tables[g] = PageTable(sub=self.sub)
         self.live[seq_id] = seq
         return seq
 
@@ -331,9 +350,9 @@ class CacheManager:
 @dataclass
 class PagedKVView:
     """What a mixer sees of a paged cache in one step."""
-    storage: object                               # [pages, 2, kv_heads, page_size, head_dim]
-    block_table: object                           # int32 [entries, width] on the device
-    page_size: int
+    storage: object                               # [kernel pages, 2, kv_heads, page_size, head_dim]
+    block_table: object                           # int32 [entries, width] on the device: kernel page ids
+    page_size: int                                # tokens of a kernel page
     writable: bool = True
     max_pages: int = 0                            # width in use this step
     tma_map: object = None                        # tensor map of `storage` for kernels that copy pages by TMA

@@ -6,15 +6,13 @@ config.json carries is ever written down in code.
 
 Parity with InfiniLM: `csrc/config/model_config.hpp:29-68` (typed getters that
 throw on a missing key or a wrong type), `csrc/config/model_config.cpp:28-57`
-(dtype from `dtype` / `torch_dtype`, rotary dim from `partial_rotary_factor`),
-`csrc/models/minicpm4/minicpm4_for_causal_lm.cpp:137-164` and
-`python/infinilm/infer_engine.py:73-100` (defaults of the MiniCPM family).
+(dtype from `dtype` / `torch_dtype`, rotary dim from `partial_rotary_factor`).
+An architecture's own configuration class lives beside its model description (`models/`).
 """
 from __future__ import annotations
 
 import dataclasses
 import json
-import math
 import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
@@ -42,7 +40,7 @@ def parse_dtype_name(name: str) -> str:
 _REQUIRED = object()
 
 
-def _take(raw: Dict[str, Any], key: str, typ, default=_REQUIRED):
+def take(raw: Dict[str, Any], key: str, typ, default=_REQUIRED):
     """Read `key` with a type check; error text names the key."""
     if key not in raw or raw[key] is None:
         if default is _REQUIRED:
@@ -105,7 +103,7 @@ class RopeScaling:
                               f"entries (short has {len(sf)}, long has {len(lf)})")
         fac = raw.get("factor")
         return RopeScaling("longrope", sf, lf,
-                           _take(raw, "original_max_position_embeddings", int),
+                           take(raw, "original_max_position_embeddings", int),
                            None if fac is None else float(fac))
 
 
@@ -127,110 +125,6 @@ class ModelConfig:
     def to_json(self) -> Dict[str, Any]:
         """The config.json content that reproduces this configuration."""
         return dict(self.raw)
-
-
-@dataclass
-class MiniCPM4Config(ModelConfig):
-    """MiniCPM4 (`MiniCPMForCausalLM`): GQA dense decoder, RMSNorm, SwiGLU,
-    RoPE/LongRoPE and muP scale factors."""
-    num_hidden_layers: int = 0
-    num_attention_heads: int = 0
-    num_key_value_heads: int = 0
-    head_dim: int = 0
-    intermediate_size: int = 0
-    rms_norm_eps: float = 0.0
-    rope_theta: float = 10000.0
-    partial_rotary_factor: float = 1.0
-    rope_scaling: RopeScaling = field(default_factory=RopeScaling)
-    scale_emb: float = 1.0
-    scale_depth: float = 1.0
-    dim_model_base: Optional[float] = None
-    attention_bias: bool = False
-    attention_output_bias: bool = False
-    mlp_bias: bool = False
-    tie_word_embeddings: bool = False
-
-    # -- derived values ---------------------------------------------------------------
-    @property
-    def rotary_dim(self) -> int:
-        """`csrc/config/model_config.cpp:41-57`."""
-        f = self.partial_rotary_factor
-        if f <= 0.0 or f >= 1.0:
-            return self.head_dim
-        r = int(round(self.head_dim * f))
-        r = min(max(r, 2), self.head_dim)
-        if r % 2:
-            r -= 1
-        return max(r, 2)
-
-    @property
-    def residual_scale(self) -> float:
-        """scale_depth / sqrt(num_hidden_layers) (`minicpm4_for_causal_lm.cpp:12-20`)."""
-        return self.scale_depth / math.sqrt(self.num_hidden_layers)
-
-    @property
-    def logit_scale(self) -> float:
-        """dim_model_base / hidden_size, 1 when the key is absent (`:117-120`)."""
-        if self.dim_model_base is None:
-            return 1.0
-        return self.dim_model_base / float(self.hidden_size)
-
-    @classmethod
-    def from_json(cls, raw: Dict[str, Any]) -> "MiniCPM4Config":
-        raw = dict(raw)
-        mt = _take(raw, "model_type", str)
-        if mt not in ("minicpm", "minicpm4"):
-            raise ConfigError(f"config.json: model_type {mt!r} is not a MiniCPM4 model")
-        if raw.get("quantization_config") is not None:
-            raise ConfigError("config.json: quantization_config is set; quantized weights are not supported")
-        archs = raw.get("architectures") or ["MiniCPMForCausalLM"]
-        hidden = _take(raw, "hidden_size", int)
-        heads = _take(raw, "num_attention_heads", int)
-        if heads <= 0 or hidden <= 0:
-            raise ConfigError("config.json: hidden_size and num_attention_heads must be positive")
-        head_dim = _take(raw, "head_dim", int, hidden // heads)
-        kv = _take(raw, "num_key_value_heads", int)
-        if kv <= 0 or heads % kv != 0:
-            raise ConfigError(f"config.json: num_attention_heads ({heads}) must be a multiple of "
-                              f"num_key_value_heads ({kv})")
-        # `bias` sets both attention_bias and mlp_bias (minicpm4_for_causal_lm.cpp:150-153).
-        if "bias" in raw and raw["bias"] is not None:
-            b = _take(raw, "bias", bool)
-            raw["attention_bias"] = b
-            raw["mlp_bias"] = b
-        dt = raw.get("dtype", raw.get("torch_dtype"))
-        if dt is None:
-            raise ConfigError("config.json: neither 'dtype' nor 'torch_dtype' is given")
-        eos = raw.get("eos_token_id", [])
-        if eos is None:
-            eos = []
-        if isinstance(eos, int):
-            eos = [eos]
-        prf = _take(raw, "partial_rotary_factor", float, 1.0)
-        cfg = cls(
-            architecture=str(archs[0]), model_type="minicpm4",
-            vocab_size=_take(raw, "vocab_size", int), hidden_size=hidden,
-            max_position_embeddings=_take(raw, "max_position_embeddings", int),
-            torch_dtype=parse_dtype_name(dt), eos_token_ids=[int(e) for e in eos], raw=raw,
-            num_hidden_layers=_take(raw, "num_hidden_layers", int),
-            num_attention_heads=heads, num_key_value_heads=kv, head_dim=head_dim,
-            intermediate_size=_take(raw, "intermediate_size", int),
-            rms_norm_eps=_take(raw, "rms_norm_eps", float),
-            rope_theta=_take(raw, "rope_theta", float, 10000.0),
-            partial_rotary_factor=prf,
-            scale_emb=_take(raw, "scale_emb", float, 1.0),
-            scale_depth=_take(raw, "scale_depth", float, 1.0),
-            dim_model_base=(None if raw.get("dim_model_base") is None
-                            else _take(raw, "dim_model_base", float)),
-            attention_bias=_take(raw, "attention_bias", bool, False),
-            attention_output_bias=_take(raw, "attention_output_bias", bool, False),
-            mlp_bias=_take(raw, "mlp_bias", bool, False),
-            tie_word_embeddings=_take(raw, "tie_word_embeddings", bool, False),
-        )
-        cfg.rope_scaling = RopeScaling.from_json(raw.get("rope_scaling"), cfg.rotary_dim)
-        if cfg.num_hidden_layers <= 0 or cfg.intermediate_size <= 0 or cfg.vocab_size <= 0:
-            raise ConfigError("config.json: num_hidden_layers, intermediate_size and vocab_size must be positive")
-        return cfg
 
 
 def read_config_json(model_dir: str) -> Dict[str, Any]:

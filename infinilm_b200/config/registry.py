@@ -82,4 +82,5 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from ..models import minicpm4  # noqa: F401  (registers itself)
+        from .. import models
+        models.register_builtin()

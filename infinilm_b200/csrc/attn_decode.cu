@@ -7,8 +7,7 @@
 //   copies (STAGES pages in flight), computes S = Q.K^T (f32), an online softmax in f32 (base 2,
 //   scale folded in), and O += P.V with P rounded to bfloat16. The four warps merge in shared
 //   memory and the block writes one partial (O unnormalised, running max, sum) per split.
-//   The block that finishes last among the splits of a (request, kv head) merges their partials and writes the
-//   bfloat16 output (found with a counter, no block waits); without a counter array a second kernel merges.
+//   A second, wide kernel merges the splits' partials and writes the bfloat16 output.
 //
 // Token t (= entry t; decode entries come first in a step) has kv length entry_kvlen[t]; its query
 // sits at position kvlen-1 and sees positions max(0, kvlen-window) .. kvlen-1 (window <= 0: all).
@@ -28,7 +27,7 @@ constexpr int AD_PAGE = 16;                       // keys per tile = page size t
 constexpr int AD_STAGES = 2;                      // 4 warps x 2 stages of a page (8-9 KB at head_dim 128): three blocks fit on an SM
 constexpr int AD_STAGE_BYTES = 2 * AD_PAGE * AT_ROW_BYTES;
 constexpr int AD_SMEM_PIPE = AD_WARPS * AD_STAGES * AD_STAGE_BYTES;
-constexpr int AD_SMEM_MERGE = (AD_WARPS * 16 * (HEAD_DIM + 4 + 2) + 16 * (HEAD_DIM + 2)) * 4;   // the warps' scaled outputs and (m, l); the block's result
+constexpr int AD_SMEM_MERGE = AD_WARPS * 16 * (HEAD_DIM + 4 + 2) * 4;   // the warps' scaled outputs and (m, l)
 constexpr int AD_SMEM = (AD_SMEM_PIPE > AD_SMEM_MERGE ? AD_SMEM_PIPE : AD_SMEM_MERGE) + AD_WARPS * AD_STAGES * 8 + 1024;
 constexpr bool AD_TMA_OK = (HEAD_DIM % 64 == 0);
 constexpr int AD_BOXES = HEAD_DIM / 64;           // 64-column boxes of a K (or V) block
@@ -114,38 +113,12 @@ __device__ __forceinline__ void ad_merge_row(float* fs, const float* o_part, con
 // (qkv, and o_part / ml_part in the merge, are written by the kernel before and read after a wait that is not the
 // kernel's first statement: they are not declared __restrict__, so that no load of them is treated as read-only
 // data and scheduled above the wait.)
-// CLUSTER 1: the splits of one (request, kv head, row tile) are the blocks of one thread-block cluster (cluster size =
-// n_splits = gridDim.x, a power of two up to 16) and merge their partial results through distributed shared memory:
-// no partials in global memory and no second kernel. Every block of a cluster passes both cluster barriers, whatever
-// its share of pages (none included) and whatever its copies did.
-__device__ __forceinline__ void ad_cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ uint32_t ad_map_peer(const void* smem_ptr, uint32_t rank) {
-    uint32_t local = (uint32_t)__cvta_generic_to_shared(smem_ptr), remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local), "r"(rank));
-    return remote;
-}
-__device__ __forceinline__ float4 ad_ld_peer4(uint32_t addr) {
-    float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ float2 ad_ld_peer2(uint32_t addr) {
-    float2 v;
-    asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
-    return v;
-}
-
-template <int CLUSTER>
 __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const __nv_bfloat16* qkv, int row_stride, const __nv_bfloat16* __restrict__ cache,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
     float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap kv_page_map,
-    int use_tma, int* __restrict__ status,
-    int* __restrict__ counters, __nv_bfloat16* __restrict__ out) {
+    int use_tma, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     // Lengths, block tables and the pages of earlier tokens do not come from the kernel before this one (it writes q and
@@ -158,6 +131,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     const int kvlen = entry_kvlen[e];
+    if (kvlen <= 0) return;                       // no keys: the merge kernel writes zeros for this row
     const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
     const int first_page = lo / AD_PAGE, last_page = (kvlen - 1) / AD_PAGE;
     // pages_per_split 0: this request's pages are divided evenly over the splits
@@ -165,10 +139,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int p0 = first_page + split * pages_per_split;
     int p1 = p0 + pages_per_split;
     if (p1 > last_page + 1) p1 = last_page + 1;
-    if (p0 > last_page) {                         // this split has no keys
-        if (!CLUSTER) return;                     // the merge kernel knows
-        p1 = p0;                                  // in a cluster it goes along with nothing to add: the barriers want every block
-    }
+    if (p0 > last_page) return;                   // this split has no keys: the merge kernel knows
 
     const int* bt = block_table + (size_t)e * bt_stride;
     const size_t page_elems = (size_t)2 * nkv * AD_PAGE * AT_HD;
@@ -194,13 +165,26 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
         }
         return __shfl_sync(0xffffffffu, my_ids, it - ids_base);
     };
+    // A block table may hold -1 (a page given back, or a caller's mistake): such a page is never dereferenced. Its
+    // copy reads page 0 instead and its keys are masked; bit (it % 32) remembers that from issue to use.
+    unsigned bad_pages = 0;
+    auto checked_page = [&](int it) {
+        int page = page_of(it);
+        if (page < 0) {
+            bad_pages |= 1u << (it & 31);
+            page = 0;
+        } else {
+            bad_pages &= ~(1u << (it & 31));
+        }
+        return page;
+    };
     // the tensor-copy pipeline of this warp; its first page is asked for now if it is not the last page of the request
     const bool tma = AD_TMA_OK && use_tma;
     const uint32_t tpipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_TMA_STAGE_BYTES;
     const uint32_t tbars = (uint32_t)__cvta_generic_to_shared(smem) + AD_WARPS * AD_STAGES * AD_TMA_STAGE_BYTES + warp * AD_STAGES * 8;
     auto tma_issue = [&](int it) {
         if (it < n_my) {
-            const int page = page_of(it);
+            const int page = checked_page(it);
             if (lane == 0) {
                 const uint32_t st = tpipe + (it % AD_STAGES) * AD_TMA_STAGE_BYTES, bar = tbars + (it % AD_STAGES) * 8;
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // the tile was read by ldmatrix before
@@ -237,12 +221,13 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     // One page: scores, online softmax, P.V. `qk` fills s[2][4] from the K tile, `pv` adds P.V from the V tile.
     auto softmax_page = [&](float (&s)[2][4], int it, uint32_t (&pf)[4]) {
         const int key0 = (p0 + warp + it * AD_WARPS) * AD_PAGE + (lane & 3) * 2;
+        const int hi = ((bad_pages >> (it & 31)) & 1) ? 0 : kvlen;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int key = key0 + nt * 8 + (j & 1);
-                s[nt][j] = (key >= lo && key < kvlen) ? s[nt][j] * scale_log2 : -INFINITY;
+                s[nt][j] = (key >= lo && key < hi) ? s[nt][j] * scale_log2 : -INFINITY;
             }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {             // h = 0: row lane/4, h = 1: row lane/4 + 8
@@ -317,7 +302,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
         const uint32_t pipe = (uint32_t)__cvta_generic_to_shared(smem) + warp * AD_STAGES * AD_STAGE_BYTES;
         auto issue = [&](int it) {
             if (it < n_my) {
-                const int page = page_of(it);
+                const int page = checked_page(it);
                 const uint32_t st = pipe + (it % AD_STAGES) * AD_STAGE_BYTES;
                 at_load_page(st, st + AD_PAGE * AT_ROW_BYTES, cache + (size_t)page * page_elems, g, nkv, AD_PAGE, 0, AD_PAGE, lane);
             }
@@ -348,8 +333,6 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     float* sm_ml = reinterpret_cast<float*>(smem);                     // [warp][16 rows][m, l]
     float* sm_o = sm_ml + AD_WARPS * 16 * 2;                           // [warp][16 rows][AT_HD + 4]
     constexpr int OS = AT_HD + 4;
-    float* res_ml = sm_o + AD_WARPS * 16 * OS;                         // [16 rows][m, l] of this block, for its cluster
-    float* res_o = res_ml + 16 * 2;                                    // [16 rows][AT_HD]
     if ((lane & 3) == 0) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -384,8 +367,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
             acc.w += v.w;
         }
         const size_t pr = ((size_t)e * nh + head0 + r) * n_splits + split;
-        if (CLUSTER) *reinterpret_cast<float4*>(res_o + (size_t)r * AT_HD + d) = acc;
-        else *reinterpret_cast<float4*>(o_part + pr * AT_HD + d) = acc;
+        *reinterpret_cast<float4*>(o_part + pr * AT_HD + d) = acc;
         if (d == 0) {
             float M = -INFINITY, L = 0.f;
 #pragma unroll
@@ -395,74 +377,13 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
                 const float mw = sm_ml[(w * 16 + r) * 2];
                 L += ((mw == -INFINITY) ? 0.f : exp2f(mw - M)) * sm_ml[(w * 16 + r) * 2 + 1];
             }
-            if (CLUSTER) {
-                res_ml[r * 2] = M;
-                res_ml[r * 2 + 1] = L;
-            } else {
-                ml_part[pr * 2] = M;
-                ml_part[pr * 2 + 1] = L;
-            }
+            ml_part[pr * 2] = M;
+            ml_part[pr * 2 + 1] = L;
         }
     }
-    if (CLUSTER) {
-        // The cluster's blocks hold one partial result each. Block `split` merges rows split, split + n_splits, ...: a
-        // warp a row, lanes over the peers for (m, l), then over the columns, every peer's four values asked for at once.
-        __syncthreads();
-        ad_cluster_sync();
-        for (int r = split + warp * n_splits; r < rows_valid; r += n_splits * AD_WARPS) {
-            float2 mlp = make_float2(-INFINITY, 0.f);
-            if (lane < n_splits) mlp = ad_ld_peer2(ad_map_peer(res_ml + r * 2, (uint32_t)lane));
-            const float M = il_warp_max(mlp.x);
-            const float f = (mlp.x == -INFINITY) ? 0.f : exp2f(mlp.x - M);
-            const float inv = 1.f / il_warp_sum(f * mlp.y);
-            float fp[16];                         // every lane gets every peer's factor here, with the whole warp present:
-#pragma unroll
-            for (int p = 0; p < 16; ++p) fp[p] = __shfl_sync(0xffffffffu, f, p);   // (the column loop below is not: lanes past head_dim / 4 skip it)
-            for (int d = lane * 4; d < AT_HD; d += 128) {
-                float4 v[16];
-#pragma unroll
-                for (int p = 0; p < 16; ++p)
-                    v[p] = p < n_splits ? ad_ld_peer4(ad_map_peer(res_o + (size_t)r * AT_HD + d, (uint32_t)p)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int p = 0; p < 16; ++p) {    // in split order
-                    acc.x += fp[p] * v[p].x;
-                    acc.y += fp[p] * v[p].y;
-                    acc.z += fp[p] * v[p].z;
-                    acc.w += fp[p] * v[p].w;
-                }
-                const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
-                *reinterpret_cast<uint2*>(out + ((size_t)e * nh + head0 + r) * AT_HD + d) = make_uint2(a, b);
-            }
-        }
-        ad_cluster_sync();                        // no block leaves while a peer may still read its results
-        return;
-    }
-    if (!counters) return;                        // the merge runs as a kernel of its own
-
-    // The block that finishes last among the splits of this (request, kv head, row tile) merges them. Every block
-    // makes its partials visible (fence), then takes a ticket; the last ticket holder sees all partials. It puts
-    // the counter back to zero for the next launch. No block waits for another.
-    __shared__ int s_last;
-    __threadfence();
-    __syncthreads();
-    const int n_valid = min(n_splits, (last_page - first_page + pages_per_split) / pages_per_split);
-    if (threadIdx.x == 0) {
-        int* cnt = counters + ((size_t)e * nkv + g) * row_tiles + rt;
-        const int ticket = atomicAdd(cnt, 1);
-        s_last = (ticket == n_valid - 1);
-        if (s_last) *cnt = 0;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    float* fs = reinterpret_cast<float*>(smem) + (size_t)warp * AD_MAX_SPLITS;    // the warps' partial tiles are done with
-    for (int r = warp; r < rows_valid; r += AD_WARPS)
-        ad_merge_row(fs, o_part, ml_part, (size_t)e * nh + head0 + r, n_valid, n_splits, out, lane);
 }
 
-// The merge as a kernel of its own (one warp per (token, head)), for callers that do not give the attention kernel
-// a counter array to find its last block with.
+// The merge: one warp per (token, head).
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_part, const float* ml_part,
                                                                 const int* __restrict__ entry_kvlen, int nh, int n_rows, int window,
                                                                 int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out) {
@@ -478,6 +399,10 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
     if (n_valid > n_splits) n_valid = n_splits;
     il_pdl_wait();
     if (row >= n_rows) return;
+    if (kvlen <= 0) {                             // no keys: the output is zero
+        for (int d = lane * 4; d < AT_HD; d += 128) *reinterpret_cast<uint2*>(out + (size_t)row * AT_HD + d) = make_uint2(0u, 0u);
+        return;
+    }
     ad_merge_row(fs[warp], o_part, ml_part, (size_t)row, n_valid, n_splits, out, lane);
 }
 
@@ -485,7 +410,7 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
 static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
                      const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
                      int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
-                     int* status = nullptr, int* counters = nullptr, int cluster = 0) {
+                     int* status = nullptr) {
     static CUtensorMap no_map;                    // passed when there is no map: the kernel does not look at it
     int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
     if (use_tma) {                                // a second map may follow the first: the page view (all zero: there is none)
@@ -498,43 +423,15 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
         if (e != cudaSuccess) return 1000 + (int)e;
         attr_set[dev] = true;
     }
     const int G = nh / nkv, row_tiles = (G + 15) / 16;
     dim3 grid(n_splits, nkv * row_tiles, n_decode);
-    if (cluster) {
-        // one cluster per (request, kv head, row tile): its blocks are the splits
-        if (n_splits > 16 || (n_splits & (n_splits - 1))) return IL_BAD_ARG;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(AD_WARPS * 32);
-        cfg.dynamicSmemBytes = AD_SMEM;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)n_splits;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[1].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = il_pdl_enabled() ? 2 : 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<1>, (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache,
-                                           block_table, bt_stride, entry_kvlen, nh, nkv, scale * 1.4426950408889634f, window, pages_per_split,
-                                           n_splits, (float*)nullptr, (float*)nullptr, use_tma ? *kv_map : no_map, page_map, use_tma, status,
-                                           (int*)nullptr, (__nv_bfloat16*)out);
-        if (e != cudaSuccess) return 1000 + (int)e;
-        IL_LAUNCH_CHECK();
-        return IL_OK;
-    }
-    IL_LAUNCH(attn_decode_kernel<0>, grid, AD_WARPS * 32, AD_SMEM, stream,
+    IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, AD_SMEM, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
-        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status, counters, (__nv_bfloat16*)out);
-    if (counters) return IL_OK;                   // merged by the last block of each group of splits
+        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status);
     const int n_rows = n_decode * nh;
     IL_LAUNCH(attn_decode_merge_kernel, (n_rows + 3) / 4, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window, pages_per_split,
                                                                   n_splits, (__nv_bfloat16*)out);
@@ -542,47 +439,35 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     return IL_OK;
 }
 
-// The largest cluster (16, 8, 4, 2 or 1 blocks) of the cluster form that this device can hold at once with this head size,
-// from the occupancy calculator; 0 if the query fails.
-IL_EXPORT int il_attn_decode_cluster_max() {
+// Blocks of the attention kernel that this device runs at once (blocks per SM from the occupancy calculator x SMs);
+// 0 if the query fails. The caller sizes the number of splits by it.
+IL_EXPORT int il_attn_decode_resident_blocks() {
     static int cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-    if (cached[dev]) return cached[dev] < 0 ? 0 : cached[dev];
-    cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM);
-    cudaFuncSetAttribute(attn_decode_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    int best = -1;
-    for (int s = 16; s >= 1 && best < 0; s >>= 1) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(s, 1, 1);
-        cfg.blockDim = dim3(AD_WARPS * 32);
-        cfg.dynamicSmemBytes = AD_SMEM;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = (unsigned)s;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, attn_decode_kernel<1>, &cfg) == cudaSuccess && n > 0) best = s;
+    if (cached[dev]) return cached[dev];
+    int per_sm = 0, sms = 0;
+    if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel, AD_WARPS * 32, AD_SMEM) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
     }
-    cudaGetLastError();
-    cached[dev] = best;
-    return best < 0 ? 0 : best;
+    cached[dev] = per_sm * sms;
+    return cached[dev];
 }
 
 // Scratch the caller provides: o_part float32 [n_decode * nh * n_splits * head_dim], ml_part [n_decode * nh * n_splits * 2].
 IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                              int bt_stride, const int* entry_kvlen, int page_size, int n_decode, int nh, int nkv, int hd,
                              float scale, int window, int pages_per_split, int n_splits, float* o_part, float* ml_part,
-                             const void* kv_map, int* status, int* counters, int cluster, cudaStream_t stream) {
+                             const void* kv_map, int* status, cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
     return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
-                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, counters, cluster);
+                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status);
 }
 
 // Writes two tensor maps (2 x 128 bytes at `out_maps`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16:

@@ -17,7 +17,9 @@
 //    with IL_NOALLOC_TOO_LARGE and nothing is launched.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress with that
 //    device current) and remembers it. That lookup is not a stream operation: make the first call
-//    on each device before any stream capture begins.
+//    on each device before any stream capture begins. Nothing locks that lookup: two host threads that
+//    make their first call on one device at the same moment both ask the runtime and both store the
+//    same address, which is harmless.
 //  * All calls share the one array. It keeps whatever the last call left there; the kernels write
 //    every partial result before they read it, so nothing has to be cleared between calls. Two
 //    calls that overlap on the GPU (different streams, no ordering between them) race on it.

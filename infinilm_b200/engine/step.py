@@ -173,7 +173,8 @@ class StepRunner:
         E = len(entries)
         groups = self.cache.groups
         paged = [g for g, grp in enumerate(groups) if grp.need.kind == "paged_kv"]
-        widths = {g: max(1, max(len(e.seq.tables[g]) for e in entries)) for g in paged}
+        sub, kpage = self.cache.sub, self.cache.kernel_page      # block tables name kernel pages: `sub` to a page
+        widths = {g: max(1, max(len(e.seq.tables[g]) for e in entries)) * sub for g in paged}
 
         # A decode-only step that wants every row can be replayed as a CUDA graph: the batch is
         # padded to a bucket of entries and of block-table width, so that the captured launches
@@ -252,7 +253,7 @@ class StepRunner:
                 rows2d = bt2d[g]
                 for k, e in enumerate(ordered):
                     tbl = e.seq.tables[g]
-                    rows2d[k, :len(tbl)] = tbl.array() if hasattr(tbl, "array") else tbl
+                    rows2d[k, :len(tbl) * sub] = tbl.array()
         else:
             for k, i in enumerate(order):
                 e = entries[i]
@@ -268,7 +269,7 @@ class StepRunner:
                 h_kvlen.append(start + n)
                 for g in paged:
                     tbl = e.seq.tables[g]
-                    bt2d[g][k, :len(tbl)] = tbl.array() if hasattr(tbl, "array") else tbl
+                    bt2d[g][k, :len(tbl) * sub] = tbl.array()
         for k in range(E, Ep):                    # padding rows: one token at position 0 of the scratch page
             a = qstart[k]
             h[s_tok[0] + a] = 0
@@ -283,7 +284,7 @@ class StepRunner:
                 w = widths[g]
                 row = h[s_bt[g][0] + k * w: s_bt[g][0] + (k + 1) * w]
                 row[:] = -1
-                row[0] = groups[g].pool.n_pages    # the scratch page behind the pool
+                row[0] = groups[g].pool.n_pages * sub    # the scratch page behind the pool
         h[s_qs[0]: s_qs[1]] = qstart
         if n_want:
             h[s_want[0]: s_want[0] + n_want] = want_rows
@@ -302,7 +303,7 @@ class StepRunner:
         def view(s):
             return dev[s[0]: s[1]]
         if graph_key is not None:                 # launch plans must not depend on this step's lengths
-            bound = min(widths[g] for g in paged) * self.cache.page_size if paged else 1
+            bound = min(widths[g] for g in paged) * kpage if paged else 1
             h_kvlen, h_qlen = [bound] * Ep, [1] * Ep
         ctx = StepContext(
             dtype=self.dtype, T=Tp, n_entries=Ep, n_decode=Ep if graph_key is not None else n_decode,
@@ -320,7 +321,7 @@ class StepRunner:
                 continue
             grp = groups[g]
             if grp.need.kind == "paged_kv":
-                caches.append(PagedKVView(grp.storage[owner], view(s_bt[g]).view(Ep, widths[g]), self.cache.page_size,
+                caches.append(PagedKVView(grp.storage[owner], view(s_bt[g]).view(Ep, widths[g]), kpage,
                                           writable=(owner == i), max_pages=widths[g], tma_map=grp.tma_maps.get(owner)))
             else:
                 caches.append(StateView(grp.storage[owner], view(s_rs), view(s_wsl), writable=(owner == i)))

@@ -254,61 +254,52 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_k: Opt
 def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      entry_kvlen: torch.Tensor, n_decode: int, page_size: int, n_heads: int, n_kv_heads: int,
                      head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
-                     o_part: Optional[torch.Tensor], ml_part: Optional[torch.Tensor], kv_map: Optional[torch.Tensor] = None,
-                     counters: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
-    """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each).
+                     o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None) -> None:
+    """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each), then the merge of
+    the splits (a second launch). A row whose length is 0 gets zeros; a block-table entry below 0 is never followed.
     pages_per_split 0: each request's pages are divided evenly over the n_splits splits.
     kv_map: the cache's tensor map from `kv_tensor_map` (pages then come in by TMA tensor copies).
-    counters: int32 zeros, one per (row, kv head, tile of 16 query heads); with it the last block of each group of
-    splits merges them (the kernel leaves the counters at zero), without it a second kernel does.
-    cluster: the splits of a request and kv head are one thread-block cluster (n_splits a power of two up to 16) and
-    merge through distributed shared memory: one launch, no scratch (o_part, ml_part may be None).
-    Scratch otherwise: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
+    Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
     _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 tensors")
-    if cluster:
-        if n_splits > CLUSTER_MAX_SPLITS or n_splits & (n_splits - 1) or counters is not None:
-            raise KernelError(f"attention_decode: a cluster takes 1, 2, 4, 8 or 16 splits, not {n_splits}")
-    else:
-        if o_part is None or ml_part is None or o_part.dtype != torch.float32 or ml_part.dtype != torch.float32:
-            raise KernelError("attention_decode: scratch must be float32")
-        need = n_decode * n_heads * n_splits
-        if o_part.numel() < need * head_dim or ml_part.numel() < need * 2:
-            raise KernelError("attention_decode: scratch too small")
+    if o_part is None or ml_part is None or o_part.dtype != torch.float32 or ml_part.dtype != torch.float32:
+        raise KernelError("attention_decode: scratch must be float32")
+    need = n_decode * n_heads * n_splits
+    if o_part.numel() < need * head_dim or ml_part.numel() < need * 2:
+        raise KernelError("attention_decode: scratch too small")
     if out.shape[1] != n_heads * head_dim or out.shape[0] < n_decode or qkv.shape[0] < n_decode:
         raise KernelError("attention_decode: out [rows, heads*head_dim]")
+    if block_table.dtype != torch.int32 or entry_kvlen.dtype != torch.int32 or block_table.shape[0] < n_decode or entry_kvlen.numel() < n_decode:
+        raise KernelError("attention_decode: block_table int32 [entries, width], entry_kvlen int32 [entries]")
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_decode", "il_attn_decode", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                               _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void_p,
-                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
-    if counters is not None:
-        n_cnt = n_decode * n_kv_heads * ((n_heads // n_kv_heads + 15) // 16)
-        if not counters.is_cuda or counters.dtype != torch.int32 or counters.numel() < n_cnt:
-            raise KernelError("attention_decode: counters must be int32 on the device, one per (row, kv head, head tile)")
+                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
     if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != KV_MAP_BYTES):
         raise KernelError("attention_decode: kv_map must be the host tensor kv_tensor_map returned")
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
-             _ptr(counters), int(cluster), _stream()), "attention_decode")
-    if counters is None and not cluster:
-        count_launches(1)                         # the merge kernel
+             _stream()), "attention_decode")
+    count_launches(1)                             # the merge kernel
 
 
-CLUSTER_MAX_SPLITS = 16
-_cluster_max = {}
+_resident = {}
 
 
-def attention_decode_cluster_max(head_dim: int) -> int:
-    """The most splits the cluster form of `attention_decode` takes on this device at this head size (a power of two up
-    to 16; 0: not at all)."""
-    if head_dim not in _cluster_max:
+def attention_decode_resident_blocks(head_dim: int) -> int:
+    """Blocks of the decode attention kernel that the current device runs at once at this head size (occupancy x SMs)."""
+    key = (torch.cuda.current_device(), head_dim)
+    if key not in _resident:
         lib = build.load("attn_decode", {"HEAD_DIM": head_dim})
-        fn = lib.il_attn_decode_cluster_max
+        fn = lib.il_attn_decode_resident_blocks
         fn.argtypes, fn.restype = [], _c_int
-        _cluster_max[head_dim] = int(fn())
-    return _cluster_max[head_dim]
+        n = int(fn())
+        if n <= 0:
+            raise KernelError("attention_decode: the occupancy query failed")
+        _resident[key] = n
+    return _resident[key]
 
 
 KV_MAP_BYTES = 384
@@ -544,27 +535,7 @@ def check_status(device) -> None:
     code = int(t.item())
     if code:
         t.zero_()
-        raise KernelError(f"a kernel's bounded wait ran out (code {code}: 11-14 gemm_tc5, 21 attn_decode, 30-39 attn_prefill_tc5, "
-                          f"others gemm_stream); the step's results are invalid")
-
-
-def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
-                bias: Optional[torch.Tensor] = None, glu: bool = False) -> None:
-    """The same product as `gemm_skinny`, weights streamed by bulk asynchronous copies (TMA) through
-    a shared-memory ring; one persistent block per SM."""
-    _need_cuda(x, w, out, bias)
-    M, K = x.shape
-    N = w.shape[0] // 2 if glu else w.shape[0]
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K or out.shape != (M, N):
-        raise KernelError(f"gemm_stream: bfloat16 x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
-        raise KernelError("gemm_stream: innermost dimension must be contiguous")
-    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.shape[0]):
-        raise KernelError("gemm_stream: bias float32, one per weight row")
-    f = _fn("gemm_stream", "il_gemm_stream", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p,
-                                              _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p])
-    _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), kind_of(out.dtype), out.stride(0), _ptr(bias), alpha,
-             M, N, K, int(glu), _ptr(stream_status(x.device)), _stream()), "gemm_stream")
+        raise KernelError(f"a kernel's bounded wait ran out (code {code}: 11-14 gemm_tc5, 21 attn_decode, 30-39 attn_prefill_tc5); the step's results are invalid")
 
 
 TC5_MAX_ROWS = 256

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import math
 import os
+import warnings
 from typing import Dict, List, Optional
 
 import torch
@@ -37,10 +38,6 @@ class Attention(Mixer):
         self.force_plain = bool(p.get("plain_kernel", False))
         self.prefill_kernel = str(p.get("prefill_kernel", os.environ.get("INFINILM_B200_PREFILL_ATTN", "auto")))   # "mma": never tcgen05
         self.fuse_rope = os.environ.get("INFINILM_B200_FUSE_ROPE", "1") != "0"
-        # The splits of a request and kv head can run as one thread-block cluster that merges through distributed shared
-        # memory (INFINILM_B200_ATTN_CLUSTER = largest cluster, 2..16). Off: the 8B decode step at batch 8 measured 3.62 ms
-        # with clusters of 16, 3.56 with 8, against 3.29 ms with the merge as a kernel of its own.
-        self.cluster_merge = int(os.environ.get("INFINILM_B200_ATTN_CLUSTER", "0"))
         self.scale = 1.0 / math.sqrt(self.hd)
         self.n_qkv = (self.nh + 2 * self.nkv) * self.hd
         self.qkv = Linear(self.hidden, self.n_qkv, dtype)
@@ -104,16 +101,30 @@ class Attention(Mixer):
                                          ctx.ws.rows("sumsq_mixer", T, (self.hidden + 15) // 16, torch.float32))
         return self.o_proj(out, ctx.ws.rows("branch", T, self.hidden, self.dtype))
 
-    # The fast bfloat16 kernels take pages of 16 keys and at most 64 query heads per kv head; anything
-    # else, and the whole float32 path, runs the plain kernel.
+    # The fast bfloat16 kernels take kernel pages of 16 keys (the cache manager lays larger pages out as runs of them)
+    # and at most 64 query heads per kv head; anything else, and the whole float32 path, runs the plain kernel.
     FAST_PAGE = 16
     FAST_MAX_GROUP = 64
-    TARGET_BLOCKS = 2 * 148                       # blocks the decode splits aim at: more splits cost more in partials than they gain
+    _warned_plain = False
+
+    WAVE_FILL = 2.0 / 3.0                         # share of the blocks the device holds at once that the splits aim at
+
+    def decode_splits(self, base: int, max_pages: int, resident: int) -> int:
+        """Splits of the keys for `base` blocks per split: as many as fill the wanted share of one wave of blocks
+        (`resident`: what the device runs at once, from the occupancy query), never more - a second, part-filled wave
+        costs more in partials than it gains - and at least four pages a split."""
+        target = max(1, int(resident * self.WAVE_FILL))
+        return max(1, min(target // base, (max_pages + 3) // 4, 128))
 
     def attend(self, qkv, out, ctx, cache) -> None:
         G = self.nh // self.nkv
         if (self.dtype != torch.bfloat16 or cache.page_size != self.FAST_PAGE or G > self.FAST_MAX_GROUP
                 or self.force_plain):
+            if self.dtype == torch.bfloat16 and not self.force_plain and not Attention._warned_plain:
+                Attention._warned_plain = True
+                warnings.warn(f"attention: pages of {cache.page_size} keys / {G} query heads per kv head are outside the fast "
+                              f"bfloat16 kernels (pages of 16 or a multiple, at most {self.FAST_MAX_GROUP} heads per kv head): "
+                              "the plain kernel runs, at a fraction of their speed", RuntimeWarning, stacklevel=2)
             ops.attention_plain(qkv, out, cache.storage, cache.block_table, ctx.tok_pos, ctx.tok_entry,
                                 cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window)
             return
@@ -124,24 +135,12 @@ class Attention(Mixer):
                 max_len = min(max_len, self.window + self.FAST_PAGE)
             max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.window is not None else 0)
             base = n_dec * self.nkv * ((G + 15) // 16)
-            # as many splits as fill one wave of blocks (two per SM), never more: a second, part-filled wave costs more
-            n_splits = max(1, min(self.TARGET_BLOCKS // base, (max_pages + 3) // 4, 128))
-            cluster_max = min(self.cluster_merge, ops.attention_decode_cluster_max(self.hd)) if self.cluster_merge else 0
-            if cluster_max > 0:
-                # the splits of a request and kv head as one thread-block cluster that merges its own partial results:
-                # a power of two, as many as the device holds in one cluster (up to 16)
-                n_splits = min(cluster_max, 1 << (n_splits.bit_length() - 1))
-                ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
-                                     self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits, None, None,
-                                     kv_map=cache.tma_map, cluster=True)
-            else:
-                rows = n_dec * self.nh * n_splits
-                ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
-                                     self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
-                                     ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
-                                     ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map)
-            # (the kernel can also merge the splits itself, in the last block of each group - `counters=` - but the
-            # merge as a second, wide launch measured faster: 3.7 against 3.9 ms for the 8B decode step at batch 8)
+            n_splits = self.decode_splits(base, max_pages, ops.attention_decode_resident_blocks(self.hd))
+            rows = n_dec * self.nh * n_splits
+            ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
+                                 self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
+                                 ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
+                                 ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map)
         if E > n_dec:
             # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128) and the cache
             # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.

@@ -70,13 +70,19 @@ def uniform01(seed: int, stream: int, counter: int) -> float:
 class Sampler:
     """Samples one token per row of logits on the device."""
 
+    RING = 4
+
     def __init__(self, device, max_rows: int = 1024):
         self.device = torch.device(device)
         self.max_rows = max_rows
-        self._host = torch.empty((4, max_rows), dtype=torch.float32, pin_memory=True)
-        self._host_np = self._host.numpy()
-        self._host_np_i = self._host.view(torch.int32).numpy()
-        self._dev = torch.empty((4, max_rows), dtype=torch.float32, device=self.device)
+        # The parameters of a step go to the device by an asynchronous copy from pinned memory. The host may fill the
+        # buffer of step k+1 before the GPU has run the copy of step k (pipelined stepping), so each step takes the
+        # next pair of a small ring (host and device), and a pair is reused only after the event recorded behind its
+        # last sampling kernel has passed.
+        self._host = [torch.empty((4, max_rows), dtype=torch.float32, pin_memory=True) for _ in range(self.RING)]
+        self._dev = [torch.empty((4, max_rows), dtype=torch.float32, device=self.device) for _ in range(self.RING)]
+        self._events: List[Optional[torch.cuda.Event]] = [None] * self.RING
+        self._turn = -1
         self._out = torch.empty(max_rows, dtype=torch.int32, device=self.device)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], uniforms: Sequence[float],
@@ -91,14 +97,20 @@ class Sampler:
             raise ValueError("sampler: rows, params and uniforms must agree (and fit max_rows)")
         if all(p.greedy for p in params):
             return self.argmax(logits, out)
-        hn = self._host_np
+        self._turn = i = (self._turn + 1) % self.RING
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        host, dev = self._host[i], self._dev[i]
+        hn = host.numpy()
         hn[0, :R] = [0.0 if p.greedy else p.temperature for p in params]
-        self._host_np_i[1, :R] = [1 if p.greedy else int(p.top_k) for p in params]
+        host.view(torch.int32).numpy()[1, :R] = [1 if p.greedy else int(p.top_k) for p in params]
         hn[2, :R] = [p.top_p for p in params]
         hn[3, :R] = list(uniforms)
-        self._dev[:, :R].copy_(self._host[:, :R], non_blocking=True)
-        ops.sample(logits, self._dev[0, :R], self._dev[1, :R].view(torch.int32), self._dev[2, :R], self._dev[3, :R],
-                   out[:R])
+        dev.copy_(host, non_blocking=True)        # whole buffers: contiguous, so a true asynchronous copy
+        ops.sample(logits, dev[0, :R], dev[1, :R].view(torch.int32), dev[2, :R], dev[3, :R], out[:R])
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[i] = ev
         return out[:R]
 
     def argmax(self, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

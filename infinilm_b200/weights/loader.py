@@ -1,8 +1,8 @@
 """Loads a model's tensors by name and hands each part its own.
 
 Every tensor the model's parts list is looked up by its checkpoint name; names and shapes are
-checked for the whole model first, and one error lists everything that is missing, unexpected
-or of the wrong shape. Storage precision is kept: bfloat16 stays bfloat16 (float16 is converted
+checked for the whole model first, and one error lists everything that is missing, unexpected,
+of the wrong shape, or of the wrong kind (integers offered for a matrix or a vector). Storage precision is kept: bfloat16 stays bfloat16 (float16 is converted
 to bfloat16), a tensor stored in 32-bit stays 32-bit, integer tables become int32. Operands of
 matrix products are then brought to the compute dtype by the parts themselves.
 
@@ -107,7 +107,7 @@ def check_against(model, source: TensorSource) -> None:
     """Compares the model's wanted tensors with what the source holds; raises one `WeightError`."""
     have = set(source.names())
     wanted = set()
-    missing, wrong = [], []
+    missing, wrong, kind = [], [], []
     for part, ws in model.weight_specs():
         full = part.full_name(ws.name)
         wanted.add(full)
@@ -120,12 +120,16 @@ def check_against(model, source: TensorSource) -> None:
                 continue
             missing.append(full)
             continue
-        _, shape = source.info(full)
+        dt, shape = source.info(full)
         if tuple(shape) != tuple(ws.shape):
             wrong.append((full, tuple(shape), tuple(ws.shape)))
+        floating = getattr(dt, "is_floating_point", None)
+        if floating is not None and floating != (ws.role != "table"):
+            kind.append(f"wrong kind of numbers: {full} is stored as {dt}, a {ws.role} needs "
+                        + ("integers" if ws.role == "table" else "floating point"))
     unexpected = sorted(have - wanted)
-    if missing or unexpected or wrong:
-        raise WeightError(sorted(missing), unexpected, wrong)
+    if missing or unexpected or wrong or kind:
+        raise WeightError(sorted(missing), unexpected, wrong, kind)
 
 
 def load_into(model, source: TensorSource, device: torch.device,

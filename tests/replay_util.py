@@ -84,3 +84,18 @@ def run_schedule(eng, requests: Dict[str, List[int]], schedule: List[List[Tuple[
             eng.cache.check_invariants()
     assert all(done[k] == len(requests[k]) for k in requests), "schedule does not cover the requests"
     return {k: torch.cat(v, 0) for k, v in outs.items()}
+
+
+def check_greedy(raw_cfg: dict, weights, prompt: List[int], tokens: List[int], dtype: str) -> None:
+    """`tokens` is a greedy continuation of `prompt` by the plain implementation: exactly in float32; in bfloat16
+    wherever the plain top-2 margin is wide enough to survive rounding (a token inside the margin is followed)."""
+    if dtype == "float32":
+        assert tokens == plain_model.greedy_generate(raw_cfg, weights, prompt, len(tokens))
+        return
+    ids = list(prompt)
+    for t in tokens:
+        lg = plain_logits(raw_cfg, weights, ids, dtype)[-1]
+        top2 = torch.topk(lg, 2).values
+        if float(top2[0] - top2[1]) > 4 * TOL[dtype] * float(lg.abs().max()):
+            assert t == int(torch.argmax(lg)), f"token {len(ids) - len(prompt)}: {t} != {int(torch.argmax(lg))}"
+        ids.append(t)

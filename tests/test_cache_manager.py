@@ -141,15 +141,17 @@ def test_random_orders_lose_nothing(seed):
     assert m.slots.n_free == 5
 
 
-def test_page_table_array_follows_the_list():
-    """The int32 array a step copies from stays equal to the list under every way the list can change."""
+@pytest.mark.parametrize("sub", [1, 2, 16])
+def test_page_table_array_follows_the_list(sub):
+    """The int32 array a step copies from stays in step with the list under every way the list can change: page p
+    stands there as the `sub` kernel pages p*sub .. p*sub+sub-1, a page given back as -1s."""
     import random
 
     import numpy as np
 
     from infinilm_b200.cache.manager import PageTable
     rng = random.Random(5)
-    t = PageTable()
+    t = PageTable(sub=sub)
     for step in range(400):
         op = rng.choice(["append"] * 6 + ["set", "set", "clear", "extend", "pop", "slice", "iadd"])
         if op == "append":
@@ -167,4 +169,22 @@ def test_page_table_array_follows_the_list():
         elif op == "iadd":
             t += [4]
         a = t.array()
-        assert a.dtype == np.int32 and a.tolist() == list(t)
+        want = [(-1 if p < 0 else p * sub + j) for p in t for j in range(sub)]
+        assert a.dtype == np.int32 and a.tolist() == want
+
+
+@pytest.mark.parametrize("page_size,kernel_page,sub", [(4, 4, 1), (16, 16, 1), (32, 16, 2), (256, 16, 16)])
+def test_pages_larger_than_the_kernels_tile_are_runs_of_kernel_pages(page_size, kernel_page, sub):
+    m = CacheManager([FULL, WIN], page_size=page_size, num_pages=6, max_seqs=2)
+    assert (m.kernel_page, m.sub) == (kernel_page, sub)
+    a = m.open("a")
+    m.reserve(a, page_size + 1)                    # two pages of each group, whatever their size
+    assert a.tables[0] == [0, 1] and m.free_pages() == {0: 4, 1: 4}
+    assert a.tables[0].array().tolist() == list(range(2 * sub))
+    m.commit(a, page_size + 1)
+    b = m.open("b")
+    m.reserve(b, 1)
+    assert b.tables[0].array().tolist() == list(range(2 * sub, 3 * sub))
+    m.close(a), m.close(b)
+    m.check_invariants()
+    assert m.free_pages() == {0: 6, 1: 6}

@@ -163,15 +163,36 @@ def test_one_error_lists_everything():
     del t["model.norm.weight"]
     t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
     t["model.layers.2.self_attn.q_proj.weight"] = torch.zeros(10, 192)
+    t["model.layers.0.mlp.down_proj.weight"] = torch.zeros(192, 320, dtype=torch.int32)      # integers offered for a matrix
+    t["model.layers.0.input_layernorm.weight"] = torch.ones(192, dtype=torch.int64)
     with pytest.raises(WeightError) as ei:
         check_against(model, DictSource(t))
     e = ei.value
     assert e.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
     assert e.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
     assert e.wrong_shape == [("model.layers.2.self_attn.q_proj.weight", (10, 192), (192, 192))]
+    assert len(e.other) == 2 and all("wrong kind of numbers" in o for o in e.other)
     msg = str(e)
-    for s in ("missing", "unexpected", "wrong shape", "up_proj", "inv_freq", "[10, 192]"):
+    for s in ("missing", "unexpected", "wrong shape", "up_proj", "inv_freq", "[10, 192]", "down_proj.weight is stored as torch.int32",
+              "input_layernorm.weight is stored as torch.int64"):
         assert s in msg
+
+
+def test_a_head_that_config_json_calls_untied_must_be_in_the_checkpoint():
+    """An absent lm_head.weight is taken from the embedding table, as InfiniLM does - unless config.json says
+    "tie_word_embeddings": false: then the checkpoint is incomplete and the error says so."""
+    raw = tiny_b()
+    assert raw["tie_word_embeddings"] is False
+    cfg, model = _model(raw)
+    t = dict(random_tensors(cfg, 0))
+    del t["lm_head.weight"]
+    with pytest.raises(WeightError) as ei:
+        check_against(model, DictSource(t))
+    assert ei.value.missing == ["lm_head.weight"]
+    raw2 = dict(raw)
+    del raw2["tie_word_embeddings"]                          # the key is absent: tied by absence of the tensor
+    _, model2 = _model(raw2)
+    check_against(model2, DictSource(t))
 
 
 def test_stored_precision_rules():

@@ -13,7 +13,7 @@ import pytest
 import torch
 
 import plain_model
-from replay_util import TOL, plain_logits, rel_err
+from replay_util import TOL, check_greedy, plain_logits, rel_err
 from tiny_configs import TINY, make_weights, random_ids, tiny_a, tiny_b
 
 pytestmark = pytest.mark.gpu
@@ -117,6 +117,94 @@ def test_graph_replay_equals_eager(cuda_device, dtype):
             assert any(g.graph is not None for g in llm.engine.runner._graphs.values())
     # reading a step's tokens one step late (the next step gets them on the device) changes nothing
     assert outs[0] == outs[1] == outs[2] == outs[3]
+    # and the four are the plain implementation's tokens, not just one another's
+    for p, toks in zip(prompts, outs[1]):
+        check_greedy(raw, w, p, toks, dtype)
+
+
+def test_sampling_parameters_of_a_step_survive_the_next_step(cuda_device):
+    """Pipelined stepping fills the sampling parameters of step k+1 on the host before the GPU has copied those of
+    step k (here the GPU is held back on purpose, as it is by a large model): every step must still draw with its own
+    uniform numbers. Eight temperature requests with eight live requests at most, so that the rows fill the buffer."""
+    raw = tiny_b()
+    w = make_weights(raw, 4)
+    cfg = config_from_json(raw)
+    prompts = [random_ids(9, raw["vocab_size"], 70 + i) for i in range(8)]
+    sp = SamplingParams(temperature=0.9, top_k=0, top_p=0.95, max_tokens=10, ignore_eos=True)
+
+    def run(pipelined, hold_back):
+        llm = LLM.from_tensors(cfg, w, dtype="float32", num_blocks=40, block_size=16, max_batch_size=8, seed=11,
+                               pipelined=pipelined)
+        assert llm.sampler.max_rows == 8
+        if hold_back:
+            step = llm.engine.step
+
+            def slow_step(entries, device_tokens=None):
+                torch.cuda._sleep(30_000_000)       # some 15 ms of GPU time in front of every step
+                return step(entries, device_tokens)
+            llm.engine.step = slow_step
+        outs = [o.outputs[0].token_ids for o in llm.generate(prompt_token_ids=prompts, sampling_params=sp)]
+        llm.close()
+        return outs
+    ref = run(False, False)
+    assert run(True, True) == ref
+    assert run(True, False) == ref
+    for i in (0, 7):
+        assert ref[i] == _plain_sampled(raw, w, prompts[i], 10, sp, 11, i)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("block_size", [None, 16])
+def test_command_line_generates_the_plain_tokens(cuda_device, tmp_path, capsys, dtype, block_size):
+    """`python -m infinilm_b200 --model DIR ...` as a user runs it: a folder written by --write-random-model, the
+    default block size (256, InfiniLM's) and 16, both precisions; the printed token ids are the plain implementation's."""
+    import warnings
+
+    from infinilm_b200.cli import main
+    raw = TINY["d"]()
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(raw))
+    model_dir = str(tmp_path / "model")
+    assert main(["--write-random-model", model_dir, "--config", str(cfg_path), "--seed", "3"]) == 0
+    from infinilm_b200.weights import random_tensors
+    w = random_tensors(config_from_json(raw), 3, "cpu")
+    prompt = random_ids(70, raw["vocab_size"], 5)
+    argv = ["--model", model_dir, "--dtype", dtype, "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "12",
+            "--batch-size", "2", "--ignore-eos", "--num-blocks", "8" if block_size is None else "64", "--log-level", "ERROR"]
+    if block_size is not None:
+        argv += ["--block-size", str(block_size)]
+    capsys.readouterr()
+    with warnings.catch_warnings():
+        warnings.filterwarnings("error", message="attention:")    # the fast kernels take both page sizes: no fallback
+        assert main(argv) == 0
+    printed = capsys.readouterr().out
+    answers = [json.loads(ln) for ln in printed.splitlines() if ln.startswith("[") and ln.endswith("]")]
+    answers = [a for a in answers if a != prompt]
+    assert len(answers) == 2 and answers[0] == answers[1] and len(answers[0]) == 12
+    check_greedy(raw, w, prompt, answers[0], dtype)
+    assert "total_time" in printed and "finish_reason: length" in printed
+
+
+def test_entry_point_loads_a_folder_at_the_default_block_size(cuda_device, tmp_path):
+    """`LLM(model_path=...)` with every default (pages of 256 tokens): the bfloat16 path stays on its fast attention
+    kernels, and a page is a run of sixteen kernel pages."""
+    import warnings
+    raw = TINY["d"]()
+    cfg = config_from_json(raw)
+    model_dir = write_model_folder(cfg, 9, str(tmp_path / "model"))
+    from infinilm_b200.weights import random_tensors
+    w = random_tensors(cfg, 9, "cpu")
+    with warnings.catch_warnings():
+        warnings.filterwarnings("error", message="attention:")
+        llm = LLM(model_dir, num_blocks=6, max_batch_size=4)
+        assert llm.engine.cache.page_size == 256 and llm.engine.cache.kernel_page == 16 and llm.engine.cache.sub == 16
+        assert llm.engine.dtype_name == "bfloat16"
+        prompts = [random_ids(n, raw["vocab_size"], 80 + n) for n in (3, 120, 260)]
+        outs = llm.generate(prompt_token_ids=prompts, sampling_params=SamplingParams(top_k=1, max_tokens=20, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        check_greedy(raw, w, p, o.outputs[0].token_ids, "bfloat16")
+    assert llm.stats()["free_pages"] == 6
+    llm.close()
 
 
 def test_preemption_recomputes_to_the_same_tokens(cuda_device):

@@ -5,6 +5,7 @@ again. In float32 and in bfloat16, on tiny configurations that differ in every s
 import pytest
 import torch
 
+import plain_model
 from replay_util import TOL, build_engine, first_bad_row, plain_logits, rel_err, run_cut, run_schedule
 from tiny_configs import TINY, make_weights, random_ids
 
@@ -118,3 +119,71 @@ def test_first_tokens(cuda_device, dtype):
         ids = random_ids(n, raw["vocab_size"], 40 + n)
         _check(run_cut(eng, ids, [n]), plain_logits(raw, w, ids, dtype), dtype, f"first {n} token(s)")
         _check(run_cut(eng, ids, [1] * n), plain_logits(raw, w, ids, dtype), dtype, f"first {n} token(s) one by one")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", [("b", 1), ("d", 3)])
+@pytest.mark.parametrize("page_size,num_pages", [(32, 9), (256, 4), (4, 60)])
+def test_mixed_requests_at_other_page_sizes(cuda_device, name, seed, dtype, page_size, num_pages):
+    """The mixed schedule with pages of 32 and 256 tokens (runs of kernel pages of 16: the fast kernels stay in use)
+    and of 4 (smaller than the kernels' tile: the plain kernels), each with a pool that forces pages to be used again."""
+    import warnings
+    raw, w = _setup(name, seed)
+    V = raw["vocab_size"]
+    lens = {"p": 3, "q": 40, "r": 70, "s": 100, "t": 55, "u": 90}
+    reqs = {k: random_ids(n, V, 50 + i) for i, (k, n) in enumerate(lens.items())}
+    sched = [
+        [("p", 3), ("q", 16)],
+        [("q", 16), ("r", 16), ("s", 2)],
+        [("q", 7), ("r", 16), ("s", 16)],
+        [("q", 1), ("r", 1), ("s", 16), ("t", 16)],
+        [("r", 1), ("s", 30), ("t", 1), ("u", 5)],
+        [("r", 36), ("s", 1), ("t", 2), ("u", 1)],
+        [("s", 35), ("t", 36), ("u", 20)],
+        [("u", 1)], [("u", 1)], [("u", 30)], [("u", 32)],
+    ]
+    with warnings.catch_warnings():
+        if page_size >= 16:
+            warnings.filterwarnings("error", message="attention:")
+        else:
+            warnings.filterwarnings("ignore", message="attention:")
+        eng = build_engine(raw, w, dtype, num_pages=num_pages, page_size=page_size)
+        assert eng.cache.kernel_page == min(page_size, 16)
+        got = run_schedule(eng, reqs, sched)
+    for k, ids in reqs.items():
+        _check(got[k], plain_logits(raw, w, ids, dtype), dtype, f"{name} mixed request {k}, pages of {page_size}")
+    assert not eng.cache.live and eng.cache.free_pages() == {0: num_pages}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,seed", CASES)
+def test_hidden_states_layer_by_layer(cuda_device, name, seed, dtype):
+    """The residual stream after every layer, taken through the step function's tap, against the plain
+    implementation's, for a whole prompt and for the same tokens cut into portions: a wrong scale, page or norm in
+    one layer is named, not just seen in the logits. (InfiniLM: hooks on intermediate tensors,
+    `csrc/debug_utils/hooks.hpp:31-62`, compared layer by layer in `test/models/llama/test_intermediate_validation.py:758-812`.)"""
+    raw, w = _setup(name, seed)
+    eng = build_engine(raw, w, dtype)
+    n = LENGTHS[name][-2]
+    ids = random_ids(n, raw["vocab_size"], 21)
+    _, hidden = plain_model.forward(raw, w, ids, round_embedding_bf16=(dtype == "bfloat16"), return_hidden=True)
+    L = raw["num_hidden_layers"]
+    for cuts in ([n], [n - 9, 1, 2, 1, 5]):
+        seen = {i: [] for i in range(L)}
+
+        def tap(label, resid, pending):
+            assert label.startswith("layer")
+            h = resid.float().clone()
+            if pending is not None:
+                branch, scale = pending
+                h += scale * branch.float()
+            seen[int(label[5:])].append(h.cpu())
+        eng.runner.tap = tap
+        try:
+            run_cut(eng, ids, cuts)
+        finally:
+            eng.runner.tap = None
+        for i in range(L):
+            got = torch.cat(seen[i], 0)
+            bad = first_bad_row(got, hidden[i + 1], TOL[dtype])
+            assert bad is None, f"{name} layer {i}, cuts {cuts}: first wrong position {bad}, rel err {rel_err(got, hidden[i + 1]):.3e}"
