@@ -223,7 +223,8 @@ class CacheManager:
                     shape = ((grp.pool.n_pages + 1) * self.sub, 2, n.n_kv_heads, self.kernel_page, n.head_dim)
                     dt = self.dtype
                 else:
-                    shape = (self.slots.n_slots,) + tuple(n.shape)
+                    # one slot more than are handed out: padding rows of a replayed step write there
+                    shape = (self.slots.n_slots + 1,) + tuple(n.shape)
                     dt = torch.float32 if n.dtype == "float32" else self.dtype
                 grp.storage[i] = torch.zeros(shape, dtype=dt, device=self.device)
                 if n.kind == "paged_kv" and dt == torch.bfloat16 and self.kernel_page == 16:
@@ -362,7 +363,7 @@ class PagedKVView:
 class StateView:
     """What a mixer sees of a state group in one step: read from `read_slots` (slot 0, the zero
     state, for a request's first step), write to `write_slots`."""
-    storage: object                               # [slots, *shape]
+    storage: object                               # [slots + 1, *shape]; the last one is scratch for padding rows
     read_slots: object                            # int32 [entries]
     write_slots: object                           # int32 [entries]
     writable: bool = True

@@ -244,7 +244,8 @@ class Scheduler:
                 break
             if r.output_token_ids and len(r.prompt_token_ids) + len(r.output_token_ids) - r.seq.length == 1:
                 toks = r.output_token_ids[-1:]    # decoding: its last token, and a page only at a page's edge
-                need = fits(r, 1) if r.seq.length % ps == 0 or len(r.seq.tables) != 1 else 0
+                # (the tables of all paged groups grow together; a model without paged groups needs none)
+                need = fits(r, 1) if r.seq.tables and r.seq.length % ps == 0 else 0
             else:
                 toks = self._next_tokens(r, budget)
                 need = fits(r, len(toks))

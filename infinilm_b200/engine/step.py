@@ -181,7 +181,7 @@ class StepRunner:
         # and the addresses they read stay the same from step to step.
         graph_key = None
         Ep, Tp = E, T
-        if (self.use_graphs and self.tap is None and n_decode == E and not self.cache.has_state
+        if (self.use_graphs and self.tap is None and n_decode == E and self.model.graph_safe
                 and all(len(e.want) == 1 for e in entries)):
             Ep = _bucket(E, _ENTRY_BUCKETS)
             widths = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
@@ -277,7 +277,7 @@ class StepRunner:
             h[s_ent[0] + a] = k
             h[s_kv[0] + k] = 1
             h[s_rs[0] + k] = 0
-            h[s_wsl[0] + k] = 0
+            h[s_wsl[0] + k] = self.cache.slots.n_slots     # the scratch slot behind those that are handed out
             h_qlen.append(1)
             h_kvlen.append(1)
             for g in paged:

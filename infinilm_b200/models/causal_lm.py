@@ -35,6 +35,8 @@ class CausalLM:
                 raise ValueError(f"run order entry {i}: cache_from must name an earlier entry that owns its cache")
         self.hidden = self.embedding.hidden
         self.vocab = self.head.vocab
+        # decode steps are replayed as CUDA graphs only if every part says it can be (`Part.graph_safe`)
+        self.graph_safe = all(p.graph_safe for p in self.parts())
 
     # -- weights ---------------------------------------------------------------------------
     def parts(self) -> List[Part]:

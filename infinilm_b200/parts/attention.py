@@ -46,6 +46,8 @@ class Attention(Mixer):
         self.position = build_part("position", pos, dtype)
         if self.position.rot_dim > self.hd:
             raise ValueError("attention: rotary dim exceeds head_dim")
+        if self.position.has_transform and self.position.rot_dim:
+            raise ValueError("attention: a position encoding is a rotary table or a transform, not both")
 
     def weight_specs(self) -> List[WeightSpec]:
         hd, H = self.hd, self.hidden
@@ -70,8 +72,12 @@ class Attention(Mixer):
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed("paged_kv", n_kv_heads=self.nkv, head_dim=self.hd, window=self.window)
 
+    @property
+    def graph_safe(self):
+        return self.position.graph_safe or not self.position.has_transform
+
     def accepts_normed(self, T):
-        return (self.dtype == torch.bfloat16 and self.fuse_rope
+        return (self.dtype == torch.bfloat16 and self.fuse_rope and not self.position.has_transform
                 and ops.skinny_rope_ok(T, self.hidden, self.hd, self.position.rot_dim))
 
     def fuses_tail(self, T):
@@ -82,7 +88,7 @@ class Attention(Mixer):
         pos = self.position
         qkv = ctx.ws.rows("qkv", T, self.n_qkv, self.dtype)
         store = cache.storage if cache.writable else None
-        if (self.dtype == torch.bfloat16 and self.fuse_rope
+        if (self.dtype == torch.bfloat16 and self.fuse_rope and not pos.has_transform
                 and ops.skinny_rope_ok(T, self.hidden, self.hd, pos.rot_dim)):
             # a few rows (decode): the projection rotates q and k and writes k, v to the cache in its epilogue
             normed = isinstance(x, ops.NormedInput)
@@ -91,6 +97,8 @@ class Attention(Mixer):
                                  pos.rot_dim, pos.inv_freq, pos.mscale, norm_in=x if normed else None)
         else:
             self.qkv(x, qkv)
+            if pos.has_transform:                 # an encoding that is no rotary table changes q and k itself
+                pos.transform(qkv, ctx, self.nh, self.nkv, self.hd)
             ops.rope_store(qkv, ctx.tok_pos, ctx.tok_entry, cache.block_table, store, cache.page_size,
                            self.nh, self.nkv, self.hd, pos.rot_dim, pos.inv_freq, pos.mscale)
         out = ctx.ws.rows("attn_out", T, self.nh * self.hd, self.dtype)

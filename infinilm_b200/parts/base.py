@@ -24,6 +24,11 @@ from .spec import CacheNeed, PartSpec, WeightSpec
 class Part:
     """Common base: parameters in, list of wanted tensors out, tensors in."""
 
+    # True: a step of single tokens through this part may be captured once and replayed as a CUDA graph - the part
+    # launches the same kernels on the same buffers whatever the step's lengths and slots, reads what changes from the
+    # step's device arrays only, and never waits for the device. A part says so itself; by default it is not replayed.
+    graph_safe = False
+
     def __init__(self, params: Dict[str, Any], prefix: str, dtype: torch.dtype):
         self.params = dict(params)
         self.prefix = prefix
@@ -60,13 +65,25 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """A position encoding that a mixer applies to its queries and keys."""
+    """A position encoding that a mixer applies to its queries and keys. Two forms:
+
+    rotary: `rot_dim`, `inv_freq`, `mscale` - a table that the mixer's fused rotate-and-store kernel applies
+      (angle = position * inv_freq[i], pairs (i, i + rot_dim/2), cos and sin times mscale);
+    any other function of (q, k, position): `has_transform = True` and `transform(qkv, ctx, ...)`, which changes the
+      q and k columns of the projected rows in place before the keys are written to the cache (rot_dim stays 0). The
+      mixer then leaves its fused projection-and-rotation kernel for the plain sequence projection, transform, store.
+    An encoding that acts on the scores (a bias per distance) is neither: it needs the attention kernels themselves."""
     rot_dim: int = 0
     mscale: float = 1.0
     inv_freq: Optional[torch.Tensor] = None     # float32 [rot_dim/2] on the device
+    has_transform = False
 
     def to_device(self, device: torch.device) -> None:
         pass
+
+    def transform(self, qkv: torch.Tensor, ctx, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+        """qkv [T, (n_heads + 2 n_kv_heads) * head_dim] in the compute dtype: change q (the first n_heads heads) and k
+        (the next n_kv_heads) in place; `ctx.tok_pos` holds each row's position (int32 on the device)."""
 
 
 class Mixer(Part):

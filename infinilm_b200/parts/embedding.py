@@ -21,6 +21,7 @@ from .spec import WeightSpec
 
 class TokenEmbedding(Part):
     """params: vocab, hidden, scale."""
+    graph_safe = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
@@ -41,6 +42,7 @@ class TokenEmbedding(Part):
 class OutputHead(Part):
     """params: vocab, hidden, scale, tied_to (full name of the embedding table or None).
     Logits are float32 on both paths."""
+    graph_safe = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)

@@ -17,6 +17,7 @@ from .spec import WeightSpec
 
 class SwiGLU(FeedForward):
     """params: hidden, intermediate, bias, out_scale."""
+    graph_safe = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)

@@ -18,6 +18,7 @@ from .spec import WeightSpec
 class RMSNorm(Norm):
     """params: size, eps."""
     fusable_rms = True
+    graph_safe = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)

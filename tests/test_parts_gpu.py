@@ -123,6 +123,64 @@ def test_attention_part_over_a_paged_cache(cuda_device, dtype, window):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_part_with_a_position_encoding_that_is_no_rotary_table(cuda_device, dtype):
+    """A position encoding defined here, in the test, that is not a rotation: q and k are scaled, dimension by
+    dimension, by 1 + a * cos(position * b_i). It is registered as a part, changes q and k through the `transform` hook
+    before the keys go into the cache, and the attention mixer and its kernels are used as they are."""
+    from infinilm_b200.parts import PositionEncoding, register_part, unregister_part
+    a_amp = 0.4
+
+    def scales(pos, hd):
+        b = 0.3 / (1.0 + torch.arange(hd, dtype=torch.float32, device=pos.device))
+        return 1.0 + a_amp * torch.cos(pos.float()[:, None] * b[None, :])
+
+    class CosScale(PositionEncoding):
+        has_transform = True
+
+        def __init__(self, params, prefix, dtype):
+            super().__init__(params, prefix, dtype)
+            self.rot_dim, self.mscale, self.inv_freq = 0, 1.0, None
+
+        def transform(self, qkv, ctx, n_heads, n_kv_heads, head_dim):
+            T = qkv.shape[0]
+            v = qkv.view(T, -1, head_dim)[:, :n_heads + n_kv_heads]
+            v.copy_((v.float() * scales(ctx.tok_pos, head_dim)[:, None, :]).to(qkv.dtype))
+    register_part("position", "test_cos_scale", CosScale)
+    try:
+        H, nh, nkv, hd = 64, 4, 2, 32
+        att = build_part("mixer", PartSpec("attention", {"hidden": H, "n_heads": nh, "n_kv_heads": nkv, "head_dim": hd,
+                                                        "position": PartSpec("test_cos_scale", {})}, "a"), DT[dtype])
+        assert not att.graph_safe and not att.accepts_normed(1)      # the transform says nothing about graph replay
+        g = torch.Generator().manual_seed(6)
+        w = {ws.name: (torch.randn(ws.shape, generator=g) * 0.15).bfloat16().float() for ws in att.weight_specs()}
+        att.set_weights({k: v.cuda() for k, v in w.items()})
+        cm = CacheManager([att.cache_need()], 16, 8, 2, device="cuda", dtype=DT[dtype])
+        T = 45
+        x = torch.randn(T, H, generator=g).to(DT[dtype])
+        seq = cm.open("r")
+        outs = []
+        for n in (30, 1, 14):                      # a portion, a single token, another portion
+            start = seq.length
+            cm.reserve(seq, start + n)
+            bt = torch.tensor([list(seq.tables[0])], dtype=torch.int32).cuda()
+            y = att.forward(x[start:start + n].cuda(), _ctx(dtype, [start], [n]),
+                            PagedKVView(cm.groups[0].storage[0], bt, 16, True, bt.shape[1]))
+            outs.append(y.clone())
+            cm.commit(seq, start + n)
+        xf = x.float()
+        q = plain_model.linear(xf, w["q_proj.weight"]).view(T, nh, hd)
+        k = plain_model.linear(xf, w["k_proj.weight"]).view(T, nkv, hd)
+        v = plain_model.linear(xf, w["v_proj.weight"]).view(T, nkv, hd)
+        sc = scales(torch.arange(T), hd)[:, None, :]
+        ref = plain_model.linear(plain_model.attention_scores(q * sc, k * sc, v), w["o_proj.weight"])
+        got = torch.cat(outs)
+        bad = first_bad_row(got, ref, TOL[dtype])
+        assert bad is None, f"first wrong position {bad}, rel err {rel_err(got, ref):.3e}"
+    finally:
+        unregister_part("position", "test_cos_scale")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T", [5, 40])
 def test_swiglu_part(cuda_device, dtype, T):
     H, I = 72, 200

@@ -25,7 +25,9 @@ from infinilm_b200.weights import random_tensors  # noqa: E402
 
 
 class DecayMixer(Mixer):
-    """y_t = s_t, s_t = decay * s_{t-1} + W x_t; s lives in a per-request state slot (float32)."""
+    """y_t = s_t, s_t = decay * s_{t-1} + W x_t; s lives in a per-request state slot (float32). A step of single
+    tokens reads and writes the slots with device-side gathers only, so it can be replayed as a graph."""
+    graph_safe = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
@@ -42,6 +44,11 @@ class DecayMixer(Mixer):
 
     def forward(self, x, ctx, cache):
         xs = x.float() @ self.w.t()
+        if ctx.n_decode == ctx.n_entries:          # one token per entry: no host loop, nothing read back
+            s = self.decay * cache.storage.index_select(0, cache.read_slots.long()) + xs
+            if cache.writable:
+                cache.storage.index_copy_(0, cache.write_slots.long(), s)
+            return s.to(x.dtype)
         out = torch.empty_like(xs)
         rs, ws = cache.read_slots.long().tolist(), cache.write_slots.long().tolist()
         a = 0
@@ -75,7 +82,10 @@ class SqrtPosition(PositionEncoding):
 
 class Top1Experts(FeedForward):
     """Every token goes to the expert with the largest router logit (f32), a SwiGLU of its own; the output is the
-    expert's, times the logit's sigmoid. A function of the token's row alone, so any cutting gives the same."""
+    expert's, times the logit's sigmoid. A function of the token's row alone, so any cutting gives the same. A step of
+    single tokens runs every expert on every row and keeps the chosen one's result (no row lists on the host), so it
+    can be replayed as a graph."""
+    graph_safe = True
 
     def __init__(self, params, prefix, dtype):
         super().__init__(params, prefix, dtype)
@@ -97,6 +107,11 @@ class Top1Experts(FeedForward):
         logits = xf @ self.w["router.weight"].t()
         top, which = logits.max(dim=1)
         out = torch.zeros_like(xf)
+        if ctx.n_decode == ctx.n_entries:
+            for e in range(self.n):
+                y = torch.nn.functional.silu(xf @ self.w[f"experts.{e}.gate.weight"].t()) * (xf @ self.w[f"experts.{e}.up.weight"].t())
+                out += (y @ self.w[f"experts.{e}.down.weight"].t()) * (torch.sigmoid(top) * (which == e))[:, None]
+            return out.to(x.dtype)
         for e in range(self.n):
             rows = (which == e).nonzero().flatten()
             if rows.numel():
@@ -261,6 +276,44 @@ def test_toy_architecture_builds_and_steps(cuda_device, toy, dtype):
         bad = first_bad_row(got[k], refs[k], tol)
         assert bad is None, f"request {k}: first wrong position {bad}"
     assert not eng.cache.live and eng.cache.slots.n_free == 4
+
+
+def test_toy_architecture_decodes_under_graph_replay(cuda_device, toy):
+    """Three requests of the toy architecture (state slots, a routed feed-forward, a layer that runs twice, a shared
+    cache) decode together with the steps replayed as CUDA graphs: the state slots and block tables come from the
+    step's device arrays, padding rows write to the scratch slot and the scratch page."""
+    sc = SCENARIOS["float32"]
+    cfg = config_from_json(RAW)
+    w = random_tensors(cfg, sc["seed"], "cpu", tie=True)
+    from infinilm_b200.engine import StepEntry
+    eng = Engine.from_tensors(cfg, w, dtype="float32", page_size=16, num_pages=24, max_seqs=4, max_batch_tokens=256)
+    assert eng.model.graph_safe and eng.cache.has_state
+    eng.enable_graphs()
+    reqs = {k: random_ids(n, 211, 30 + i) for i, (k, n) in enumerate({"a": 44, "b": 31, "c": 57}.items())}
+    refs = {k: plain_toy(w, r, False) for k, r in reqs.items()}
+    n_dec = 24
+    seqs = {k: eng.open(k) for k in reqs}
+    got = {k: [] for k in reqs}
+    for k, r in reqs.items():                      # prompts: eager steps
+        n = len(r) - n_dec
+        got[k].append(eng.step([StepEntry(seqs[k], r[:n], list(range(n)))]).clone())
+    for j in range(n_dec):                         # three single tokens a step (padded to a bucket of four): replayed
+        ks = list(reqs)
+        lg = eng.step([StepEntry(seqs[k], [reqs[k][len(reqs[k]) - n_dec + j]], [0]) for k in ks]).clone()
+        for i, k in enumerate(ks):
+            got[k].append(lg[i:i + 1])
+    assert any(g.graph is not None for g in eng.runner._graphs.values()), "no step was replayed"
+    for k in reqs:
+        out = torch.cat(got[k], 0)
+        bad = first_bad_row(out, refs[k], 2e-5)
+        assert bad is None, f"request {k}: first wrong position {bad}, rel err {rel_err(out, refs[k]):.3e}"
+        eng.close(seqs[k])
+    eng.synchronize()
+    # the zero state (slot 0) was never written, whatever the padding rows did
+    for grp in eng.cache.groups:
+        if grp.need.kind == "state":
+            for st in grp.storage.values():
+                assert float(st[0].abs().max()) == 0.0
 
 
 def test_toy_experts_all_used(toy):
