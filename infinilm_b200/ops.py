@@ -573,3 +573,4 @@ def gemm_tc5_scratch_bytes(M: int, N: int, K: int) -> int:
 
 def tc5_ok(M: int, K: int) -> bool:
     return SKINNY_MAX_ROWS < M <= TC5_MAX_ROWS and K % 8 == 0
+
