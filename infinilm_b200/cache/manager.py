@@ -161,7 +161,7 @@ class PageTable(list):
         return self._arr[:n * self.sub]
 
 
-@dataclass
+@dataclass(eq=False)                              # a request's cache is itself: compared by identity
 class SequenceCache:
     """What the cache holds for one request."""
     seq_id: object

@@ -111,6 +111,8 @@ class StepRunner:
         self.h2d_bytes = 0
         self.steps_run = 0
         self.tokens_run = 0
+        self._last_decode: Optional["_DecodeBatch"] = None    # the replayed decode step just run, if the next may follow it
+        self.fast_steps = 0
 
     # -- descriptor buffers ----------------------------------------------------------------
     def _desc(self, n_ints: int):
@@ -129,6 +131,82 @@ class StepRunner:
             ev.synchronize()
         return self._desc_ring[self._desc_i], self._desc_dev
 
+    # -- a decode step that follows the same decode step ----------------------------------------
+    def _follow_decode(self, last: "_DecodeBatch", entries: Sequence[StepEntry], device_tokens) -> Optional[torch.Tensor]:
+        """The step after a replayed decode-only step, if it is the same requests in the same order with one token each
+        (what a serving run is mostly made of): nothing is built per request but its token; lengths and positions
+        advance as columns, a block table row is rewritten only where a request begins a page, the same graph is
+        replayed. Returns None when the step is anything else; the general path then runs (and reports what is wrong
+        with a batch that is wrong). With hundreds of live requests the general path cost the host more per step than
+        the GPU needed to run it."""
+        E = last.E
+        if len(entries) != E or self.tap is not None or not self.use_graphs:
+            return None
+        gs = last.gs
+        if gs.graph is None or gs.ws_version != self.ws.version:
+            return None
+        seqs = last.seqs
+        for e, s in zip(entries, seqs):
+            if e.seq is not s or len(e.tokens) != 1 or len(e.want) != 1:
+                return None
+        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=E)
+        lens = last.lens
+        neg = tokens < 0
+        if int(tokens.max()) >= self.model.vocab or (neg.any() and (device_tokens is None or int(-1 - tokens.min()) >= device_tokens.numel())):
+            return None
+        max_pos = getattr(self, "max_positions", None)
+        if max_pos is not None and int(lens.max()) + 1 > max_pos:
+            return None
+        cache, sub, ps = self.cache, self.cache.sub, self.cache.page_size
+        starts = np.flatnonzero(lens % ps == 0)   # these requests' next token begins a page
+        paged = list(last.widths)
+        for i in starts:
+            for g in paged:
+                if (len(seqs[i].tables[g]) + 1) * sub > last.widths[g]:
+                    return None                   # the table outgrows this graph's width: the general path picks the next
+        if starts.size:
+            if not cache.can_reserve([(seqs[i], int(lens[i]) + 1) for i in starts]):
+                return None                       # (the general path raises OutOfPages)
+            for i in starts:
+                cache.reserve(seqs[i], int(lens[i]) + 1)
+        m, sp = last.mirror, last.spans
+        m[sp["tok"][0]: sp["tok"][0] + E] = np.maximum(tokens, 0)
+        m[sp["pos"][0]: sp["pos"][0] + E] = lens
+        m[sp["kv"][0]: sp["kv"][0] + E] = lens + 1
+        m[sp["rs"][0]: sp["rs"][0] + E] = m[sp["wsl"][0]: sp["wsl"][0] + E]       # no request is at its first step any more
+        for i in starts:
+            for g in paged:
+                tbl = seqs[i].tables[g]
+                a = sp["bt"][g][0] + int(i) * last.widths[g]
+                m[a: a + len(tbl) * sub] = tbl.array()
+        rows = np.flatnonzero(neg)
+        n_patch = int(rows.size)
+        if n_patch:
+            m[sp["prow"][0]: sp["prow"][0] + n_patch] = rows
+            m[sp["psrc"][0]: sp["psrc"][0] + n_patch] = -1 - tokens[rows]
+        n = last.n_ints
+        host, _ = self._desc(n)
+        host.numpy()[:n] = m
+        dev = gs.desc
+        dev[:n].copy_(host[:n], non_blocking=True)
+        if n_patch:
+            ops.patch_tokens(dev[sp["tok"][0]: sp["tok"][1]], dev[sp["prow"][0]: sp["prow"][0] + n_patch],
+                             dev[sp["psrc"][0]: sp["psrc"][0] + n_patch], device_tokens)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._desc_events[self._desc_i] = ev
+        self.h2d_bytes += 4 * n
+        gs.graph.replay()
+        ops.count_launches(gs.n_kernels)
+        for s_ in seqs:                           # what CacheManager.commit does for a request without a window
+            s_.length += 1
+        last.lens = lens + 1
+        self._last_decode = last
+        self.steps_run += 1
+        self.tokens_run += E
+        self.fast_steps += 1
+        return gs.logits[:E]
+
     # -- the step ----------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the order of
@@ -138,6 +216,11 @@ class StepRunner:
         (int32 on the device, e.g. what the sampler drew in the step before) when the step runs."""
         if not entries:
             return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.device)
+        last, self._last_decode = self._last_decode, None
+        if last is not None:
+            logits = self._follow_decode(last, entries, device_tokens)
+            if logits is not None:
+                return logits
         vocab = self.model.vocab
         seen = set()
         T = 0
@@ -349,6 +432,12 @@ class StepRunner:
             if gs.graph is not None:
                 gs.graph.replay()
                 ops.count_launches(gs.n_kernels)
+                if not any(grp.need.kind == "paged_kv" and grp.need.window is not None for grp in groups):
+                    # the next step may be the same requests with one more token each: keep what it can start from
+                    self._last_decode = _DecodeBatch(
+                        seqs=[e.seq for e in entries], gs=gs, E=E, Ep=Ep, widths=dict(widths), mirror=h[:off].copy(),
+                        lens=np.fromiter((e.seq.length + 1 for e in entries), dtype=np.int32, count=E),
+                        spans=dict(tok=s_tok, pos=s_pos, kv=s_kv, rs=s_rs, wsl=s_wsl, bt=dict(s_bt), prow=s_prow, psrc=s_psrc), n_ints=off)
             logits = gs.logits
             # rows of the logits follow the sorted entries; give them back in the caller's order
             if any(row_of_entry[i] != i for i in range(E)):
@@ -361,6 +450,21 @@ class StepRunner:
         self.steps_run += 1
         self.tokens_run += T
         return logits
+
+
+@dataclass
+class _DecodeBatch:
+    """A replayed decode-only step, kept so that the step after it - the same requests in the same order, one more
+    token each - is made from it: lengths go up by one, block tables change only where a request starts a page."""
+    seqs: list
+    gs: "_GraphSlot"
+    E: int
+    Ep: int
+    widths: Dict[int, int]
+    mirror: np.ndarray                            # the step's descriptors as they went to the device
+    lens: np.ndarray                              # cached tokens per request after that step
+    spans: dict
+    n_ints: int
 
 
 _ENTRY_BUCKETS = [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512]

@@ -165,7 +165,8 @@ class LLM:
         ev = None
         if rows:
             params = [e.request.params for e in rows]
-            us = [uniform01(e.request.params.seed if e.request.params.seed is not None else self.seed,
+            us = [0.0 if e.request.params.greedy else                       # a greedy row draws nothing
+                  uniform01(e.request.params.seed if e.request.params.seed is not None else self.seed,
                             e.request.sample_stream, len(e.request.output_token_ids)) for e in rows]
             self.sampler.sample(logits, params, us, out=ids_dev)
             host[:len(rows)].copy_(ids_dev[:len(rows)], non_blocking=True)
