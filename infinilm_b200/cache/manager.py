@@ -109,6 +109,7 @@ class PageTable(list):
         self._arr = np.empty(max(16, 2 * len(self)) * self.sub, dtype=np.int32)
         self._stale = len(self) > 0
         self._steps = np.arange(self.sub, dtype=np.int32)
+        self._addr_of, self._addr = None, 0       # the array whose address `_addr` is
 
     def _put(self, i: int, p: int) -> None:
         sub = self.sub
@@ -148,6 +149,18 @@ class PageTable(list):
     reverse, sort = _touched("reverse"), _touched("sort")
     __delitem__, __iadd__, __imul__ = _touched("__delitem__"), _touched("__iadd__"), _touched("__imul__")
     del _touched
+
+    @property
+    def n_kernel_pages(self) -> int:
+        return len(self) * self.sub
+
+    def address(self) -> int:
+        """Host address of the kernel page ids (int32, `n_kernel_pages` of them), for native code; valid until the table changes."""
+        if self._stale:
+            self.array()
+        if self._addr_of is not self._arr:        # (taking .ctypes.data costs a microsecond: once per array)
+            self._addr_of, self._addr = self._arr, self._arr.ctypes.data
+        return self._addr
 
     def array(self) -> np.ndarray:
         """The kernel page ids as int32 [len * sub]; a view, valid until the table changes."""

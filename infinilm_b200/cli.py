@@ -19,6 +19,20 @@ import time
 logger = logging.getLogger("infinilm_b200")
 
 
+def parse_list(value: str):
+    """An int or a list of ints, in InfiniLM's spellings (`python/infinilm/base_config.py:11-43`): "1", "[1,2,4]", "1,2,4"."""
+    value = value.strip()
+    try:
+        if value.startswith("[") and value.endswith("]"):
+            got = json.loads(value)
+            return [int(x) for x in got] if isinstance(got, list) else int(got)
+        if "," in value:
+            return [int(x.strip()) for x in value.split(",")]
+        return int(value)
+    except (ValueError, TypeError):
+        raise argparse.ArgumentTypeError(f"value must be an int or list[int], got: {value}") from None
+
+
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="infinilm_b200", description=__doc__,
                                 formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -38,6 +52,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--batch-size", type=int, default=1, help="copies of the prompt to generate for")
     p.add_argument("--max-batch-size", type=int, default=8, help="maximum number of live requests")
     p.add_argument("--max-new-tokens", type=int, default=512, help="maximum number of new tokens to generate")
+    p.add_argument("--input-len", type=parse_list, default=10, help="input sequence length(s) of the benchmark tool: 256 | 256,1024 | [256,1024]")
+    p.add_argument("--output-len", type=parse_list, default=20, help="output sequence length(s) of the benchmark tool")
     p.add_argument("--prompt", type=str, default="How are you", help="default prompt text")
     p.add_argument("--top-k", type=int, default=1)
     p.add_argument("--top-p", type=float, default=1.0)
@@ -117,6 +133,70 @@ def main(argv=None) -> int:
         print(f"(finish_reason: {o.finish_reason.value if o.finish_reason else None})\n")
         n_new += len(o.outputs[0].token_ids)
     print(f"total_time: {round((t2 - t1) * 1000, 2)} ms, {n_new} new tokens, {n_new / max(t2 - t1, 1e-9):.1f} tok/s")
+    return 0
+
+
+def bench_main(argv=None) -> int:
+    """The benchmark tool in InfiniLM's manner (`examples/bench.py:592-696,731-745`): for every combination of
+    --input-len and --output-len at --batch-size, generate for that many copies of a prompt and print the time to the first
+    token and the prefill and decode throughputs as InfiniLM defines them (`python/infinilm/infer_engine.py:720-726`:
+    prefill tok/s = batch * input_len / time of the first step(s); decode tok/s = batch * (n - 1) / time of the others).
+    The prompt is seeded random token ids of the asked length (InfiniLM repeats a text to length; random weights have no text)."""
+    args = build_parser().parse_args(argv)
+    logging.basicConfig(level=getattr(logging, args.log_level), format="%(asctime)s - %(name)s - %(levelname)s - %(message)s")
+    if not args.model:
+        print("--model is required", file=sys.stderr)
+        return 2
+    import torch
+
+    from .llm import LLM, SamplingParams
+    ins = args.input_len if isinstance(args.input_len, list) else [args.input_len]
+    outs = args.output_len if isinstance(args.output_len, list) else [args.output_len]
+    device = "cuda" if args.device in ("auto", "nvidia") else args.device
+    need_pages = args.batch_size * ((max(ins) + max(outs) + args.block_size - 1) // args.block_size + 1)
+    llm = LLM(args.model, device=device, dtype=args.dtype, max_batch_size=max(args.max_batch_size, args.batch_size),
+              max_tokens=max(outs), num_blocks=max(args.num_blocks, need_pages), block_size=args.block_size,
+              enable_graph=args.enable_graph, attn_backend=args.attn, skip_load=args.skip_load,
+              max_num_batched_tokens=args.max_num_batched_tokens, chunk_size=args.chunk_size, seed=args.seed, admission=args.admission)
+    results = []
+    try:
+        for n_in in ins:
+            for n_out in outs:
+                if n_in + n_out > llm.model_config.max_position_embeddings:
+                    print(f"[bench] input_len={n_in} + output_len={n_out} passes max_position_embeddings; skipped")
+                    continue
+                g = torch.Generator().manual_seed(args.seed + n_in)
+                ids = torch.randint(0, llm.model_config.vocab_size, (n_in,), generator=g).tolist()
+                sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k, max_tokens=n_out, ignore_eos=True)
+                for timed in ([False, True] if args.warmup else [True]):
+                    reqs = [llm.add_request(ids, sp if timed else SamplingParams(top_k=1, max_tokens=min(4, n_out), ignore_eos=True))
+                            for _ in range(args.batch_size)]
+                    torch.cuda.synchronize()
+                    t0 = time.perf_counter()
+                    while any(len(r.output_token_ids) < 1 for r in reqs):       # the prompts' steps, to every request's first token
+                        llm.step()
+                    torch.cuda.synchronize()
+                    t1 = time.perf_counter()
+                    while not all(r.finished for r in reqs):
+                        llm.step()
+                    torch.cuda.synchronize()
+                    t2 = time.perf_counter()
+                if any(len(r.output_token_ids) != n_out for r in reqs):
+                    print("[bench] a request did not produce output_len tokens", file=sys.stderr)
+                    return 1
+                B = args.batch_size
+                rec = {"batch_size": B, "input_len": n_in, "output_len": n_out, "ttft_ms": (t1 - t0) * 1e3,
+                       "prefill_tok_s": B * n_in / (t1 - t0),
+                       "itl_ms": (t2 - t1) * 1e3 / max(n_out - 1, 1), "decode_tok_s": B * (n_out - 1) / (t2 - t1) if n_out > 1 else 0.0}
+                results.append(rec)
+                print(f"\n Generation completed in {round((t2 - t0) * 1000, 2)} ms")
+                print(f" Batchsize={B}  Per_Batch_Input_Len={n_in}  Per_Batch_New_Tokens={n_out}")
+                print(f" Prefill TTFT: {round(rec['ttft_ms'], 2)} ms  Throughput: {round(rec['prefill_tok_s'], 2)} tok/s")
+                if n_out > 1:
+                    print(f" Decode  Avg ITL: {round(rec['itl_ms'], 2)} ms   Throughput: {round(rec['decode_tok_s'], 2)} tok/s")
+    finally:
+        llm.close()
+    print(json.dumps({"bench": results}))
     return 0
 
 

@@ -2,7 +2,7 @@
 
 Each `.cu` file becomes one shared object with `extern "C"` entry points; it is
 compiled with plain `nvcc` (no torch headers, so a file takes seconds) the first
-time something asks for it, and kept under `_build/` beside the sources, keyed by
+time something asks for it (a `.cpp` file is host code and goes through `g++`), and kept under `_build/` beside the sources, keyed by
 a hash of the source text, the included headers, the macro definitions and the
 compiler flags. Nothing here falls back to another implementation: a missing
 compiler or a failed compile raises.
@@ -104,11 +104,23 @@ def _env_flags() -> Tuple[str, ...]:
     return tuple(os.environ.get("INFINILM_B200_NVCC_FLAGS", "").split())
 
 
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def source_path(name: str) -> str:
+    """`<name>.cu` (device code, nvcc) or `<name>.cpp` (host code, g++)."""
+    for ext in (".cu", ".cpp"):
+        p = os.path.join(_HERE, name + ext)
+        if os.path.isfile(p):
+            return p
+    raise BuildError(f"no source {os.path.join(_HERE, name)}.cu or .cpp")
+
+
 def so_path(name: str, defines: Optional[Dict[str, object]] = None,
             extra_flags: Tuple[str, ...] = ()) -> str:
     extra_flags = tuple(extra_flags) + _env_flags()
     dfs = tuple(sorted((k, str(v)) for k, v in (defines or {}).items()))
-    src = os.path.join(_HERE, name + ".cu")
+    src = source_path(name)
     tag = "".join(f"-{k}{v}" for k, v in dfs)
     return os.path.join(build_dir(), f"{name}{tag}-{_key(src, dfs, tuple(extra_flags))}.so")
 
@@ -116,20 +128,23 @@ def so_path(name: str, defines: Optional[Dict[str, object]] = None,
 def compile_source(name: str, defines: Optional[Dict[str, object]] = None,
                    extra_flags: Tuple[str, ...] = (), verbose: bool = False) -> str:
     """Compile `<name>.cu` if its shared object is not there yet; returns the path."""
-    src = os.path.join(_HERE, name + ".cu")
-    if not os.path.isfile(src):
-        raise BuildError(f"no CUDA source {src}")
+    src = source_path(name)
     out = so_path(name, defines, extra_flags)
     if os.path.isfile(out):
         return out
-    nvcc = find_nvcc()
     dfs = [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [nvcc] + ARCH_FLAGS + BASE_FLAGS + list(extra_flags) + list(_env_flags()) + dfs + ["-I", _HERE, "-o", tmp, src]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    _say(f"compiling {name}.cu {' '.join(dfs)} for sm_100a ...")
+    if src.endswith(".cpp"):
+        gxx = shutil.which(os.environ.get("CXX", "g++")) or shutil.which("g++")
+        if gxx is None:
+            raise BuildError("g++ was not found: the host code of infinilm_b200 cannot be built")
+        cmd = [gxx] + HOST_FLAGS + dfs + ["-I", _HERE, "-o", tmp, src]
+    else:
+        cmd = [find_nvcc()] + ARCH_FLAGS + BASE_FLAGS + list(extra_flags) + list(_env_flags()) + dfs + ["-I", _HERE, "-o", tmp, src]
+        if verbose:
+            cmd.insert(1, "-Xptxas")
+            cmd.insert(2, "-v")
+    _say(f"compiling {os.path.basename(src)} {' '.join(dfs)}" + ("" if src.endswith(".cpp") else " for sm_100a") + " ...")
     t0 = time.time()
     env = dict(os.environ)
     env.setdefault("TMPDIR", build_dir())       # nvcc scratch files: HOME may not exist
@@ -138,7 +153,7 @@ def compile_source(name: str, defines: Optional[Dict[str, object]] = None,
 
     def beat():
         while not done.wait(10.0):
-            _say(f"  still compiling {name}.cu ({time.time() - t0:.0f} s)")
+            _say(f"  still compiling {os.path.basename(src)} ({time.time() - t0:.0f} s)")
     th = threading.Thread(target=beat, daemon=True)
     th.start()
     log, _ = proc.communicate()
@@ -148,7 +163,7 @@ def compile_source(name: str, defines: Optional[Dict[str, object]] = None,
             os.unlink(tmp)
         except OSError:
             pass
-        raise BuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n{' '.join(cmd)}\n{log}")
+        raise BuildError(f"the compiler failed on {os.path.basename(src)} (exit {proc.returncode}):\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
     _say(f"  built {os.path.basename(out)} in {time.time() - t0:.1f} s")
     if verbose and log:
@@ -173,4 +188,4 @@ def load(name: str, defines: Optional[Dict[str, object]] = None,
 
 
 def all_sources():
-    return sorted(fn[:-3] for fn in os.listdir(_HERE) if fn.endswith(".cu"))
+    return sorted(os.path.splitext(fn)[0] for fn in os.listdir(_HERE) if fn.endswith((".cu", ".cpp")))

@@ -14,6 +14,7 @@ the device in one copy, and the head runs only on the wanted rows.
 """
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence
 
@@ -221,43 +222,66 @@ class StepRunner:
             logits = self._follow_decode(last, entries, device_tokens)
             if logits is not None:
                 return logits
+        # ---- checks on whole columns (a fault is then looked up entry by entry, for the message) ------------------
         vocab = self.model.vocab
-        seen = set()
-        T = 0
+        E = len(entries)
+        seqs = [e.seq for e in entries]
+        n_tok = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=E)
+        start = np.fromiter((s_.length for s_ in seqs), dtype=np.int32, count=E)
+        T = int(n_tok.sum())
+        if int(n_tok.min()) < 1:
+            i = int(np.argmin(n_tok))
+            raise StepError(f"entry {i} ({seqs[i].seq_id!r}) brings no token")
+        if len(set(map(id, seqs))) != E:
+            seen = set()
+            for s_ in seqs:
+                if id(s_) in seen:
+                    raise StepError(f"request {s_.seq_id!r} appears twice in one step")
+                seen.add(id(s_))
+        tokens = np.fromiter(itertools.chain.from_iterable(e.tokens for e in entries), dtype=np.int64, count=T)
+        tok_off = np.zeros(E + 1, dtype=np.int32)
+        np.cumsum(n_tok, out=tok_off[1:])
+        lo, hi = int(tokens.min()), int(tokens.max())
+        if hi >= vocab or (lo < 0 and device_tokens is None):
+            t = int(np.argmax(tokens >= vocab)) if hi >= vocab else int(np.argmax(tokens < 0))
+            i = int(np.searchsorted(tok_off, t, side="right")) - 1
+            raise StepError(f"request {seqs[i].seq_id!r}: token id outside [0, {vocab})")
+        if lo < 0 and -1 - lo >= device_tokens.numel():
+            i = int(np.searchsorted(tok_off, int(np.argmin(tokens)), side="right")) - 1
+            raise StepError(f"request {seqs[i].seq_id!r}: device token {-1 - lo} does not exist")
         max_pos = getattr(self, "max_positions", None)
-        for i, e in enumerate(entries):
-            n = len(e.tokens)
-            if n < 1:
-                raise StepError(f"entry {i} ({e.seq.seq_id!r}) brings no token")
-            if id(e.seq) in seen:
-                raise StepError(f"request {e.seq.seq_id!r} appears twice in one step")
-            seen.add(id(e.seq))
-            for w in e.want:
-                if not 0 <= w < n:
-                    raise StepError(f"entry {i} ({e.seq.seq_id!r}): wanted place {w} is outside its {n} tokens")
-            hi, lo = (e.tokens[0], e.tokens[0]) if n == 1 else (max(e.tokens), min(e.tokens))
-            if hi >= vocab or (lo < 0 and device_tokens is None):
-                raise StepError(f"request {e.seq.seq_id!r}: token id outside [0, {vocab})")
-            if max_pos is not None and e.seq.length + n > max_pos:
-                raise StepError(f"request {e.seq.seq_id!r} would pass max_position_embeddings {max_pos}")
-            T += n
+        if max_pos is not None and int((start + n_tok).max()) > max_pos:
+            i = int(np.argmax(start + n_tok))
+            raise StepError(f"request {seqs[i].seq_id!r} would pass max_position_embeddings {max_pos}")
         if T > self.max_batch_tokens:
             raise StepError(f"step of {T} tokens exceeds max_batch_tokens {self.max_batch_tokens}")
+        n_want_of = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=E)
+        want_off = np.zeros(E + 1, dtype=np.int32)
+        np.cumsum(n_want_of, out=want_off[1:])
+        want = np.fromiter(itertools.chain.from_iterable(e.want for e in entries), dtype=np.int32, count=int(want_off[E]))
+        if want.size:
+            bad = (want < 0) | (want >= np.repeat(n_tok, n_want_of))
+            if bad.any():
+                j = int(np.argmax(bad))
+                i = int(np.searchsorted(want_off, j, side="right")) - 1
+                raise StepError(f"entry {i} ({seqs[i].seq_id!r}): wanted place {int(want[j])} is outside its {int(n_tok[i])} tokens")
         # Reserve pages for all entries, or for none.
-        if not self.cache.can_reserve([(e.seq, e.seq.length + len(e.tokens)) for e in entries]):
+        new_len = (start + n_tok).tolist()
+        if not self.cache.can_reserve(list(zip(seqs, new_len))):
             raise OutOfPages("the step needs more pages than are free: "
                              + ", ".join(f"{e.seq.seq_id!r}+{len(e.tokens)}" for e in entries))
-        for e in entries:
-            self.cache.reserve(e.seq, e.seq.length + len(e.tokens))
+        for s_, n_ in zip(seqs, new_len):
+            self.cache.reserve(s_, n_)
 
         # Single decoded tokens first, prompt portions after; the wanted rows keep the caller's order.
-        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
-        n_decode = sum(1 for e in entries if len(e.tokens) == 1)
-        E = len(entries)
+        order = np.argsort(n_tok != 1, kind="stable").astype(np.int32)
+        n_decode = int((n_tok == 1).sum())
         groups = self.cache.groups
         paged = [g for g, grp in enumerate(groups) if grp.need.kind == "paged_kv"]
         sub, kpage = self.cache.sub, self.cache.kernel_page      # block tables name kernel pages: `sub` to a page
-        widths = {g: max(1, max(len(e.seq.tables[g]) for e in entries)) * sub for g in paged}
+        tbl_len = np.array([[len(s_.tables[g]) * sub for s_ in seqs] for g in paged], dtype=np.int32).reshape(len(paged), E)
+        tbl_ptr = np.array([[s_.tables[g].address() for s_ in seqs] for g in paged], dtype=np.uint64).reshape(len(paged), E)
+        widths = {g: max(1, int(tbl_len[k].max())) for k, g in enumerate(paged)}
 
         # A decode-only step that wants every row can be replayed as a CUDA graph: the batch is
         # padded to a bucket of entries and of block-table width, so that the captured launches
@@ -265,35 +289,14 @@ class StepRunner:
         graph_key = None
         Ep, Tp = E, T
         if (self.use_graphs and self.tap is None and n_decode == E and self.model.graph_safe
-                and all(len(e.want) == 1 for e in entries)):
+                and int(n_want_of.min()) == 1 and int(n_want_of.max()) == 1):
             Ep = _bucket(E, _ENTRY_BUCKETS)
             widths = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
             Tp = Ep
             graph_key = (Ep, tuple(sorted(widths.items())))
-        qstart = [0] * (Ep + 1)
-        row_of_entry = {}
-        for k, i in enumerate(order):
-            row_of_entry[i] = k
-            qstart[k + 1] = qstart[k] + len(entries[i].tokens)
-        for k in range(E, Ep):
-            qstart[k + 1] = qstart[k] + 1
-        want_rows: List[int] = []
-        for i, e in enumerate(entries):
-            base = qstart[row_of_entry[i]]
-            want_rows.extend(base + w for w in e.want)
-        if graph_key is not None:
-            want_rows = list(range(Ep))           # row k of the logits belongs to sorted entry k
-        n_want = len(want_rows)
-
-        patches = []                              # (token row, index into device_tokens)
-        if device_tokens is not None:
-            for i, e in enumerate(entries):
-                for j, t in enumerate(e.tokens):
-                    if t < 0:
-                        if -1 - t >= device_tokens.numel():
-                            raise StepError(f"request {e.seq.seq_id!r}: device token {-1 - t} does not exist")
-                        patches.append((qstart[row_of_entry[i]] + j, -1 - t))
-        n_patch = Tp if graph_key is not None else len(patches)       # a replayed step's buffer is sized once, for any number
+        n_want = Ep if graph_key is not None else int(want_off[E])
+        n_neg = int((tokens < 0).sum())
+        n_patch = Tp if graph_key is not None else n_neg          # a replayed step's buffer is sized once, for any number
         n_ints = (3 * Tp + (Ep + 1) + Ep + max(n_want, 1) + 2 * Ep + sum(Ep * w for w in widths.values()) + 2 * n_patch)
         host, dev = self._desc(n_ints)
         if graph_key is not None:
@@ -302,82 +305,38 @@ class StepRunner:
                 gs = self._graphs[graph_key] = _GraphSlot(torch.empty(n_ints, dtype=torch.int32, device=self.device))
             dev = gs.desc
         h = host.numpy()
-        off = 0
-
-        def take(n):
-            nonlocal off
-            v = (off, off + n)
-            off += n
-            return v
-        s_tok, s_pos, s_ent = take(Tp), take(Tp), take(Tp)
-        s_qs, s_kv, s_want, s_rs, s_wsl = take(Ep + 1), take(Ep), take(max(n_want, 1)), take(Ep), take(Ep)
-        s_bt = {g: take(Ep * widths[g]) for g in paged}
-        s_prow, s_psrc = take(n_patch), take(n_patch)
-        h_qlen, h_kvlen = [], []
-        bt2d = {g: h[s_bt[g][0]: s_bt[g][1]].reshape(Ep, widths[g]) for g in paged}
+        # ---- the descriptors, filled by native code (csrc/step_fill.cpp) --------------------------------------------
+        slots = np.fromiter((s_.state_slot for s_ in seqs), dtype=np.int32, count=E)
+        fresh = np.fromiter((s_.fresh_state for s_ in seqs), dtype=np.uint8, count=E)
+        w_arr = np.array([widths[g] for g in paged], dtype=np.int32)
+        scratch = np.array([groups[g].pool.n_pages * sub for g in paged], dtype=np.int32)
+        offs = np.zeros(12, dtype=np.int32)
+        outs = np.zeros(3, dtype=np.int32)          # patches, wanted rows, entry at fault
+        rc = ops.step_fill(h, host.numel(), E, Ep, Tp, order, n_tok, start, slots, fresh, tokens, tok_off, w_arr, tbl_ptr, tbl_len,
+                           scratch, self.cache.slots.n_slots, want, want_off, graph_key is not None, n_patch, offs, outs)
+        if rc != 0:
+            i = int(outs[2])
+            who = f"entry {i} ({seqs[i].seq_id!r})" if i >= 0 else "the step"
+            raise StepError({-11: f"{who}: a wanted place is outside its {int(n_tok[i]) if i >= 0 else 0} tokens",
+                             -12: f"{who}: its block table is wider than the step's", -13: "the step's descriptors outgrew their buffer",
+                             -14: f"{who}: more device tokens than the step has room for"}.get(rc, f"step_fill failed ({rc})"))
+        n_patches = int(outs[0])
+        o = offs.tolist()
+        off = o[11]
+        s_tok, s_pos, s_ent = (o[0], o[0] + Tp), (o[1], o[1] + Tp), (o[2], o[2] + Tp)
+        s_qs, s_kv, s_want = (o[3], o[3] + Ep + 1), (o[4], o[4] + Ep), (o[5], o[5] + max(n_want, 1))
+        s_rs, s_wsl = (o[6], o[6] + Ep), (o[7], o[7] + Ep)
+        s_bt, a_ = {}, o[8]
         for g in paged:
-            bt2d[g][:E].fill(-1)
-        if n_decode == E:
-            # every entry brings one token (the steps a serving run is mostly made of): whole columns at once, nothing
-            # per entry but its block table, copied from the array the cache keeps beside it
-            ordered = [entries[i] for i in order]
-            lens = np.fromiter((e.seq.length for e in ordered), dtype=np.int32, count=E)
-            h[s_tok[0]: s_tok[0] + E] = np.maximum(np.fromiter((e.tokens[0] for e in ordered), dtype=np.int64, count=E), 0)
-            h[s_pos[0]: s_pos[0] + E] = lens
-            h[s_ent[0]: s_ent[0] + E] = np.arange(E, dtype=np.int32)
-            h[s_kv[0]: s_kv[0] + E] = lens + 1
-            slots = np.fromiter((e.seq.state_slot for e in ordered), dtype=np.int32, count=E)
-            h[s_wsl[0]: s_wsl[0] + E] = slots
-            fresh = np.fromiter((e.seq.fresh_state for e in ordered), dtype=bool, count=E)
-            h[s_rs[0]: s_rs[0] + E] = np.where(fresh, 0, slots)
-            h_qlen = [1] * E
-            h_kvlen = (lens + 1).tolist()
-            for g in paged:
-                rows2d = bt2d[g]
-                for k, e in enumerate(ordered):
-                    tbl = e.seq.tables[g]
-                    rows2d[k, :len(tbl) * sub] = tbl.array()
-        else:
-            for k, i in enumerate(order):
-                e = entries[i]
-                n, start = len(e.tokens), e.seq.length
-                a, b = qstart[k], qstart[k + 1]
-                h[s_tok[0] + a: s_tok[0] + b] = np.maximum(np.asarray(e.tokens, dtype=np.int64), 0)
-                h[s_pos[0] + a: s_pos[0] + b] = np.arange(start, start + n, dtype=np.int32)
-                h[s_ent[0] + a: s_ent[0] + b] = k
-                h[s_kv[0] + k] = start + n
-                h[s_rs[0] + k] = 0 if e.seq.fresh_state else e.seq.state_slot
-                h[s_wsl[0] + k] = e.seq.state_slot
-                h_qlen.append(n)
-                h_kvlen.append(start + n)
-                for g in paged:
-                    tbl = e.seq.tables[g]
-                    bt2d[g][k, :len(tbl) * sub] = tbl.array()
-        for k in range(E, Ep):                    # padding rows: one token at position 0 of the scratch page
-            a = qstart[k]
-            h[s_tok[0] + a] = 0
-            h[s_pos[0] + a] = 0
-            h[s_ent[0] + a] = k
-            h[s_kv[0] + k] = 1
-            h[s_rs[0] + k] = 0
-            h[s_wsl[0] + k] = self.cache.slots.n_slots     # the scratch slot behind those that are handed out
-            h_qlen.append(1)
-            h_kvlen.append(1)
-            for g in paged:
-                w = widths[g]
-                row = h[s_bt[g][0] + k * w: s_bt[g][0] + (k + 1) * w]
-                row[:] = -1
-                row[0] = groups[g].pool.n_pages * sub    # the scratch page behind the pool
-        h[s_qs[0]: s_qs[1]] = qstart
-        if n_want:
-            h[s_want[0]: s_want[0] + n_want] = want_rows
-        if patches:
-            h[s_prow[0]: s_prow[0] + len(patches)] = [p[0] for p in patches]
-            h[s_psrc[0]: s_psrc[0] + len(patches)] = [p[1] for p in patches]
+            s_bt[g] = (a_, a_ + Ep * widths[g])
+            a_ += Ep * widths[g]
+        s_prow, s_psrc = (o[9], o[9] + n_patch), (o[10], o[10] + n_patch)
+        h_qlen = n_tok[order].tolist() + [1] * (Ep - E)
+        h_kvlen = (start + n_tok)[order].tolist() + [1] * (Ep - E)
         dev[:off].copy_(host[:off], non_blocking=True)
-        if patches:                               # tokens the host has not seen: copied in on the device
-            ops.patch_tokens(dev[s_tok[0]: s_tok[1]], dev[s_prow[0]: s_prow[0] + len(patches)],
-                             dev[s_psrc[0]: s_psrc[0] + len(patches)], device_tokens)
+        if n_patches:                             # tokens the host has not seen: copied in on the device
+            ops.patch_tokens(dev[s_tok[0]: s_tok[1]], dev[s_prow[0]: s_prow[0] + n_patches],
+                             dev[s_psrc[0]: s_psrc[0] + n_patches], device_tokens)
         ev = torch.cuda.Event()
         ev.record()
         self._desc_events[self._desc_i] = ev
@@ -435,18 +394,12 @@ class StepRunner:
                 if not any(grp.need.kind == "paged_kv" and grp.need.window is not None for grp in groups):
                     # the next step may be the same requests with one more token each: keep what it can start from
                     self._last_decode = _DecodeBatch(
-                        seqs=[e.seq for e in entries], gs=gs, E=E, Ep=Ep, widths=dict(widths), mirror=h[:off].copy(),
-                        lens=np.fromiter((e.seq.length + 1 for e in entries), dtype=np.int32, count=E),
+                        seqs=seqs, gs=gs, E=E, Ep=Ep, widths=dict(widths), mirror=h[:off].copy(), lens=start + 1,
                         spans=dict(tok=s_tok, pos=s_pos, kv=s_kv, rs=s_rs, wsl=s_wsl, bt=dict(s_bt), prow=s_prow, psrc=s_psrc), n_ints=off)
             logits = gs.logits
-            # rows of the logits follow the sorted entries; give them back in the caller's order
-            if any(row_of_entry[i] != i for i in range(E)):
-                idx = torch.tensor([row_of_entry[i] for i in range(E)], device=self.device)
-                logits = logits.index_select(0, idx)
-            else:
-                logits = logits[:E]
-        for e in entries:
-            self.cache.commit(e.seq, e.seq.length + len(e.tokens))
+            logits = logits[:E]                   # (all entries bring one token: the running order is the caller's)
+        for s_, n_ in zip(seqs, new_len):
+            self.cache.commit(s_, n_)
         self.steps_run += 1
         self.tokens_run += T
         return logits

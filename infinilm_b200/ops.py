@@ -574,3 +574,39 @@ def gemm_tc5_scratch_bytes(M: int, N: int, K: int) -> int:
 def tc5_ok(M: int, K: int) -> bool:
     return SKINNY_MAX_ROWS < M <= TC5_MAX_ROWS and K % 8 == 0
 
+
+
+# ----------------------------------------------------------------------------------------------
+def _np_ptr(a) -> _c_void_p:
+    return _c_void_p(a.ctypes.data)
+
+
+def step_fill(out, out_cap: int, E: int, Ep: int, Tp: int, order, n_tok, start, slot, fresh, tokens, tok_off, widths, tbl_ptr,
+              tbl_len, scratch_page, scratch_slot: int, want, want_off, graph_mode: bool, n_patch_cap: int, offsets, outs) -> int:
+    """Native host code (csrc/step_fill.cpp): fills a step's descriptors into the int32 host array `out` from columns
+    given as numpy arrays (int32 unless said: `fresh` uint8, `tokens` int64, `tbl_ptr` uint64 addresses of the block
+    tables' arrays). `offsets` (int32 [12]) receives where each part starts, `outs` (int32 [3]) the number of device
+    tokens, of wanted rows, and the entry at fault. Returns 0 or the negative code of the fault."""
+    for name, a, dt in (("order", order, "int32"), ("n_tok", n_tok, "int32"), ("start", start, "int32"), ("slot", slot, "int32"),
+                        ("fresh", fresh, "uint8"), ("tokens", tokens, "int64"), ("tok_off", tok_off, "int32"),
+                        ("widths", widths, "int32"), ("tbl_ptr", tbl_ptr, "uint64"), ("tbl_len", tbl_len, "int32"),
+                        ("scratch_page", scratch_page, "int32"), ("want", want, "int32"), ("want_off", want_off, "int32"),
+                        ("offsets", offsets, "int32"), ("outs", outs, "int32"), ("out", out, "int32")):
+        if a.dtype.name != dt or not a.flags["C_CONTIGUOUS"]:
+            raise KernelError(f"step_fill: {name} must be a contiguous {dt} array")
+    if (len(order) != E or len(n_tok) != E or len(start) != E or len(slot) != E or len(fresh) != E or len(tok_off) != E + 1
+            or len(want_off) != E + 1 or tbl_ptr.size != widths.size * E or tbl_len.size != widths.size * E
+            or scratch_page.size != widths.size or offsets.size < 12 or outs.size < 3 or out.size < out_cap):
+        raise KernelError("step_fill: array sizes do not match the number of entries and groups")
+    lib = build.load("step_fill")
+    f = lib.il_step_fill
+    if not getattr(f, "_sig", False):
+        f.argtypes = ([_c_void_p, ctypes.c_longlong, _c_int, _c_int, _c_int] + [_c_void_p] * 7 + [_c_int] + [_c_void_p] * 4 + [_c_int]
+                      + [_c_void_p] * 2 + [_c_int, _c_int] + [_c_void_p] * 4)
+        f.restype = _c_int
+        f._sig = True
+    return int(f(_np_ptr(out), out_cap, E, Ep, Tp, _np_ptr(order), _np_ptr(n_tok), _np_ptr(start), _np_ptr(slot), _np_ptr(fresh),
+                 _np_ptr(tokens), _np_ptr(tok_off), int(widths.size), _np_ptr(widths), _np_ptr(tbl_ptr), _np_ptr(tbl_len),
+                 _np_ptr(scratch_page), scratch_slot, _np_ptr(want), _np_ptr(want_off), int(graph_mode), n_patch_cap,
+                 _c_void_p(offsets.ctypes.data), _c_void_p(outs.ctypes.data), _c_void_p(outs.ctypes.data + 4),
+                 _c_void_p(outs.ctypes.data + 8)))

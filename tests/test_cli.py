@@ -30,6 +30,18 @@ def test_option_names_of_infinilm_parse():
         build_parser().parse_args(["--model", "/m", "--attn", "other"])
 
 
+def test_length_lists_of_the_benchmark_tool_parse_as_infinilm_spells_them():
+    from infinilm_b200.cli import parse_list
+    assert parse_list("7") == 7 and parse_list("[1,2,4]") == [1, 2, 4] and parse_list("256, 1024") == [256, 1024]
+    import argparse
+    with pytest.raises(argparse.ArgumentTypeError):
+        parse_list("a,b")
+    a = build_parser().parse_args(["--model", "/m", "--input-len", "256,1024", "--output-len", "[16]", "--batch-size", "8"])
+    assert a.input_len == [256, 1024] and a.output_len == [16]
+    d = build_parser().parse_args(["--model", "/m"])
+    assert (d.input_len, d.output_len) == (10, 20)              # InfiniLM's defaults
+
+
 def test_write_random_model_and_missing_arguments(tmp_path, capsys):
     cfg_path = tmp_path / "c.json"
     cfg_path.write_text(json.dumps(tiny_b()))

@@ -187,6 +187,21 @@ def test_command_line_generates_the_plain_tokens(cuda_device, tmp_path, capsys, 
     assert "total_time" in printed and "finish_reason: length" in printed
 
 
+def test_benchmark_tool_sweeps_lengths(cuda_device, tmp_path, capsys):
+    """`examples/bench.py` (InfiniLM's benchmark tool): lists of input and output lengths at a batch size, one record a case."""
+    from infinilm_b200.cli import bench_main
+    raw = TINY["d"]()
+    model_dir = write_model_folder(config_from_json(raw), 4, str(tmp_path / "model"))
+    capsys.readouterr()
+    assert bench_main(["--model", model_dir, "--batch-size", "3", "--input-len", "20,150", "--output-len", "[5,9]", "--block-size", "16",
+                       "--num-blocks", "64", "--enable-graph", "--log-level", "ERROR"]) == 0
+    out = capsys.readouterr().out
+    recs = json.loads([ln for ln in out.splitlines() if ln.startswith('{"bench"')][0])["bench"]
+    assert [(r["input_len"], r["output_len"], r["batch_size"]) for r in recs] == [(20, 5, 3), (20, 9, 3), (150, 5, 3), (150, 9, 3)]
+    assert all(r["prefill_tok_s"] > 0 and r["decode_tok_s"] > 0 and r["ttft_ms"] > 0 for r in recs)
+    assert out.count("Prefill TTFT:") == 4 and out.count("Decode  Avg ITL:") == 4
+
+
 def test_entry_point_loads_a_folder_at_the_default_block_size(cuda_device, tmp_path):
     """`LLM(model_path=...)` with every default (pages of 256 tokens): the bfloat16 path stays on its fast attention
     kernels, and a page is a run of sixteen kernel pages."""

@@ -187,3 +187,46 @@ def test_hidden_states_layer_by_layer(cuda_device, name, seed, dtype):
             got = torch.cat(seen[i], 0)
             bad = first_bad_row(got, hidden[i + 1], TOL[dtype])
             assert bad is None, f"{name} layer {i}, cuts {cuts}: first wrong position {bad}, rel err {rel_err(got, hidden[i + 1]):.3e}"
+
+
+def test_step_refuses_batches_that_cannot_be_run(cuda_device):
+    """What the step function checks on the host before anything is launched (these checks stand where a memory checker
+    would): a request twice in a step, no token, a token id outside the vocabulary, a token that is said to be on the device
+    when nothing is, a wanted place outside the entry's tokens, a step beyond the token budget or the model's maximum
+    length, more pages than the pool has. After every refusal the cache is as it was."""
+    from infinilm_b200.cache import OutOfPages
+    from infinilm_b200.engine import StepEntry
+    from infinilm_b200.engine.step import StepError
+    raw, w = _setup("a", 0)
+    eng = build_engine(raw, w, "float32", num_pages=4, max_batch_tokens=40)
+    V = raw["vocab_size"]
+    a, b = eng.open("a"), eng.open("b")
+    cases = [
+        ([StepEntry(a, [1, 2], [0]), StepEntry(a, [3], [0])], StepError, "twice"),
+        ([StepEntry(a, [], [])], StepError, "no token"),
+        ([StepEntry(a, [1, V], [0])], StepError, "outside"),
+        ([StepEntry(a, [1, -1], [0])], StepError, "outside"),
+        ([StepEntry(a, [1, 2, 3], [3])], StepError, "wanted place"),
+        ([StepEntry(a, [1] * 30, []), StepEntry(b, [2] * 11, [])], StepError, "max_batch_tokens"),
+        ([StepEntry(a, [1] * 40, []), ], None, None),                                     # fine: 40 tokens, 3 pages
+        ([StepEntry(b, [1] * 33, [])], OutOfPages, "pages"),                              # 3 more pages, 1 is free
+    ]
+    for entries, exc, word in cases:
+        before = (a.length, b.length, eng.cache.free_pages())
+        if exc is None:
+            eng.step(entries)
+            continue
+        with pytest.raises(exc, match=word):
+            eng.step(entries)
+        assert (a.length, b.length, eng.cache.free_pages()) == before
+        eng.cache.check_invariants()
+    with pytest.raises(StepError, match="device token"):
+        eng.step([StepEntry(b, [-5], [0])], device_tokens=torch.zeros(2, dtype=torch.int32, device="cuda"))
+    eng.close(a), eng.close(b)
+    c = eng.open("c")
+    eng2 = build_engine(raw, w, "float32", num_pages=16, max_batch_tokens=200)
+    d = eng2.open("d")
+    eng2.step([StepEntry(d, [1] * 120, [])])
+    with pytest.raises(StepError, match="max_position_embeddings"):
+        eng2.step([StepEntry(d, [1] * 9, [])])                                            # 129 > 128
+    eng.close(c), eng2.close(d)
