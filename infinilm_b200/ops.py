@@ -535,7 +535,7 @@ def check_status(device) -> None:
     code = int(t.item())
     if code:
         t.zero_()
-        raise KernelError(f"a kernel's bounded wait ran out (code {code}: 11-14 gemm_tc5, 21 attn_decode, 30-39 attn_prefill_tc5); the step's results are invalid")
+        raise KernelError(f"a kernel's bounded wait ran out (code {code}: 11-14 gemm_tc5, 21 attn_decode, 30-39 attn_prefill_tc5, 51-54 gemm_mid); the step's results are invalid")
 
 
 TC5_MAX_ROWS = 256
@@ -574,6 +574,33 @@ def gemm_tc5_scratch_bytes(M: int, N: int, K: int) -> int:
 def tc5_ok(M: int, K: int) -> bool:
     return SKINNY_MAX_ROWS < M <= TC5_MAX_ROWS and K % 8 == 0
 
+
+
+MID_MAX_ROWS = 128
+
+
+def mid_ok(M: int, K: int) -> bool:
+    return SKINNY_MAX_ROWS < M <= MID_MAX_ROWS and K % 8 == 0
+
+
+def gemm_mid(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0, bias: Optional[torch.Tensor] = None,
+             glu: bool = False, nb: int = 0, bm: int = 0) -> None:
+    """out[M,N] = alpha * x[M,K] @ w[N,K]^T (+ bias) for 17..128 bfloat16 rows on the tcgen05 tensor cores: tiles of 64
+    or 128 weight rows (`bm`; the A operand) by blocks of `nb` activation rows (0: chosen by the kernel) over all of K; out bfloat16
+    or float32. glu: w is [2N,K] (gate rows, then up rows) and out[M,N] = silu(gate) * up (bfloat16)."""
+    _need_cuda(x, w, out, bias)
+    M, K = x.shape
+    N = w.shape[0] // 2 if glu else w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_mid: bfloat16 x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_mid: innermost dimension must be contiguous")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.shape[0]):
+        raise KernelError("gemm_mid: bias float32, one per weight row")
+    f = _fn("gemm_mid", "il_gemm_mid", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_float,
+                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), kind_of(out.dtype), out.stride(0), _ptr(bias), alpha,
+             M, N, K, int(glu), nb, bm, _ptr(stream_status(x.device)), _stream()), "gemm_mid")
 
 
 # ----------------------------------------------------------------------------------------------

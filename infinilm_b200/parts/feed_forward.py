@@ -61,8 +61,14 @@ class SwiGLU(FeedForward):
                                              ctx.ws.rows("xw_ffn", T, self.hidden, self.dtype),
                                              ctx.ws.rows("sumsq_ffn", T, (self.hidden + 15) // 16, torch.float32))
             return self.down(act, ctx.ws.rows("branch", T, self.hidden, self.dtype))
-        gu = self.gate_up(x, ctx.ws.rows("gate_up", T, 2 * self.inter, self.dtype))
         act = ctx.ws.rows("ffn_act", T, self.inter, self.dtype)
+        if self.dtype == torch.bfloat16 and ops.mid_ok(T, self.hidden):
+            # 17..128 rows: gate and up on the tcgen05 tensor cores as two accumulators in the same lanes, SiLU(gate)*up in
+            # the epilogue (measured against the library product followed by the SwiGLU kernel at 8B sizes: 44.6 against
+            # 48.4 us at 32 rows, 47.6 against 49.9 at 64, 52.5 against 57.6 at 128)
+            ops.gemm_mid(x, self.gate_up.weight, act, 1.0, self.gate_up.bias, glu=True)
+            return self.down(act, ctx.ws.rows("branch", T, self.hidden, self.dtype))
+        gu = self.gate_up(x, ctx.ws.rows("gate_up", T, 2 * self.inter, self.dtype))
         ops.swiglu(gu, act)
         return self.down(act, ctx.ws.rows("branch", T, self.hidden, self.dtype))
 

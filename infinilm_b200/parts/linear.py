@@ -4,8 +4,8 @@ Parity with InfiniLM: `csrc/layers/linear/base_linear.cpp:35-44` and
 `csrc/layers/quantization/none_quantization.cpp:26-46` (weight [out,in], optional bias, a scale
 `alpha` passed into the product). The float32 path runs the FFMA kernel of this package. On the
 bfloat16 path up to 16 rows (decode) run this package's weight-streaming kernel, 17 to 256 rows run
-its tcgen05/TMA kernel where that is enabled (the output head), and everything else calls the
-library matrix product, as InfiniLM does for its linears.
+its tcgen05/TMA kernels where that is enabled (the output head: `gemm_mid` up to 64 rows, `gemm_tc5`
+beyond), and everything else calls the library matrix product, as InfiniLM does for its linears.
 """
 from __future__ import annotations
 
@@ -18,6 +18,8 @@ from .. import ops
 
 
 class Linear:
+    MID_ROWS = 64                                 # up to here `gemm_mid` measured faster than `gemm_tc5` on the vocabulary-sized head
+
     def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, alpha: float = 1.0, use_tc5: bool = False):
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.alpha = dtype, float(alpha)
@@ -44,6 +46,10 @@ class Linear:
         if ops.skinny_ok(x.shape[0], self.in_features):
             # a few rows (decode): the weight-streaming kernel of this package
             ops.gemm_skinny(x, self.weight, out, self.alpha, self.bias)
+            return out
+        if self.use_tc5 and x.shape[0] <= self.MID_ROWS and ops.mid_ok(x.shape[0], self.in_features):
+            # 17..64 rows: tiles of weight rows by blocks of activation rows over all of K, nothing cut along K
+            ops.gemm_mid(x, self.weight, out, self.alpha, self.bias)
             return out
         if self.use_tc5 and ops.tc5_ok(x.shape[0], self.in_features) and (out_f32 or out.dtype == torch.bfloat16):
             if self._tc5_scratch is None:

@@ -555,3 +555,48 @@ def test_gemm_tc5(cuda_device, M, N, K, out_dtype):
     close(out, ref.float(), "float32" if out_dtype == "float32" else "bfloat16")
     ops.gemm_tc5(x, w, out, 1.0, None, scratch)
     close(out, (x.double() @ w.double().t()).float(), "float32" if out_dtype == "float32" else "bfloat16")
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 97, 64), (32, 128, 72), (64, 331, 200), (128, 513, 1000), (64, 4608, 4096), (33, 300, 264),
+                                   (40, 4096, 16384)])
+@pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("bm,nb", [(0, 0), (64, 16), (128, 32)])
+def test_gemm_mid(cuda_device, M, N, K, out_dtype, bm, nb):
+    """The tcgen05 product of 17..128 rows (tiles of 64 or 128 weight rows by blocks of activation rows, all of K in one
+    unit, two issuing threads with an accumulator each) against a float64 reference, row by row."""
+    g = torch.Generator(device="cuda").manual_seed(13)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=DT[out_dtype])
+    ops.gemm_mid(x, w, out, 0.7, b, nb=nb, bm=bm)
+    torch.cuda.synchronize()
+    assert int(ops.stream_status("cuda:0").item()) == 0
+    ref = 0.7 * (x.double() @ w.double().t()) + b.double()
+    close(out, ref.float(), "float32" if out_dtype == "float32" else "bfloat16")
+    ops.gemm_mid(x, w, out, 1.0, None, nb=nb, bm=bm)
+    close(out, (x.double() @ w.double().t()).float(), "float32" if out_dtype == "float32" else "bfloat16")
+
+
+@pytest.mark.parametrize("M,I,K", [(20, 160, 72), (64, 264, 200), (48, 1000, 520), (128, 320, 192), (64, 16384, 4096)])
+@pytest.mark.parametrize("bm,nb", [(0, 0), (64, 32), (128, 16)])
+def test_gemm_mid_swiglu(cuda_device, M, I, K, bm, nb):
+    g = torch.Generator(device="cuda").manual_seed(14)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2 * I, K, device="cuda", generator=g) * 2 / math.sqrt(K)).bfloat16()
+    b = torch.randn(2 * I, device="cuda", generator=g) * 0.1
+    out = torch.full((M, I), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gemm_mid(x, w, out, 1.0, b, glu=True, nb=nb, bm=bm)
+    torch.cuda.synchronize()
+    assert int(ops.stream_status("cuda:0").item()) == 0
+    y = x.double() @ w.double().t() + b.double()
+    close(out, (torch.nn.functional.silu(y[:, :I]) * y[:, I:]).float(), "bfloat16")
+    ops.gemm_mid(x, w, out, 1.0, None, glu=True, nb=nb, bm=bm)
+    y = x.double() @ w.double().t()
+    close(out, (torch.nn.functional.silu(y[:, :I]) * y[:, I:]).float(), "bfloat16")
+    # against the library product and the SwiGLU kernel it replaces on 17..128 rows (which round gate and up to bfloat16 first)
+    gu = torch.empty(M, 2 * I, device="cuda", dtype=torch.bfloat16)
+    torch.mm(x, w.t(), out=gu)
+    act = torch.empty(M, I, device="cuda", dtype=torch.bfloat16)
+    ops.swiglu(gu, act)
+    close(out, act.float(), "bfloat16")
