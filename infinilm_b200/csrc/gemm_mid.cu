@@ -13,9 +13,9 @@
 //
 //   Blocks are persistent (one per SM) and take units b, b + G, ... Roles by warp: warp 0 issues TMA tensor copies
 //   (128-byte swizzle) into a ring of stages - the first ring of weight tiles before the dependent-launch wait, since
-//   weights do not come from the kernel before -, warps 1 and 2 issue tcgen05.mma, each into an accumulator of its own, and
-//   commit (two accumulator sets alternate, so a unit's epilogue overlaps the next unit's products), warps 3-6 read their
-//   lanes of tensor memory and finish.
+//   weights do not come from the kernel before -, warps 1-4 issue tcgen05.mma (two or four of them), each into an accumulator
+//   of its own, and commit (two accumulator sets alternate, so a unit's epilogue overlaps the next unit's products), warps 5-8
+//   read their lanes of tensor memory and finish.
 //
 //   Every mbarrier wait is bounded; one that runs out sets *status, the roles leave their loops, the block frees its
 //   tensor memory and returns.
@@ -27,7 +27,7 @@ constexpr int GM_BK = 64;                         // K per tensor copy: 128 byte
 constexpr int GM_KBLK = 4;                        // copies (of each operand) per stage, at most: the issuing thread pays some 400 clocks
                                                   // per stage for its wait and commit, which 12 KB a stage did not cover (20 GB/s an SM)
 constexpr int GM_MAX_STAGES = 6;
-constexpr int GM_THREADS = 224;                   // producer, two issuers, four epilogue warps
+constexpr int GM_THREADS = 288;                   // producer, up to four issuers, four epilogue warps
 constexpr int GM_MAX_ROWS = 128;
 constexpr unsigned GM_SPIN_LIMIT = 1u << 26;
 
@@ -49,6 +49,10 @@ __device__ __forceinline__ bool gm_mbar_wait(uint32_t bar, uint32_t parity) {
         if (done) return true;
     }
     return false;
+}
+__device__ __forceinline__ void gm_tma_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void gm_tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
@@ -76,10 +80,13 @@ __device__ __forceinline__ void gm_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 
 enum { GM_PLAIN = 0, GM_GLU = 1 };
 
+
 struct GmParams {
     int M, N, K;                                  // N: output columns (SwiGLU: the intermediate size; W has 2N rows)
     int mode, n_acc;                              // accumulators per unit: 1 plain, 2 SwiGLU (gate, up)
     int NB, n_bb;                                 // activation rows per unit (a multiple of 16), blocks of them
+    int n_issuers;                                // threads that issue products, each into an accumulator of its own
+    int tma3d;                                    // the tensor maps are the three-dimensional ones (K a multiple of 64)
     int n_tiles, n_chunks, n_stages, n_units, kblk, bm;   // kblk: 64-wide blocks of K per stage; bm: W rows per tile
     int ldo, out_kind;
     float alpha;
@@ -109,17 +116,18 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_mid_kernel(const __grid_co
     const uint32_t tfull0 = empty0 + GM_MAX_STAGES * 8, tempty0 = tfull0 + 2 * 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x, b = blockIdx.x;
-    const int acc_cols = 2 * p.NB;                // tensor-memory columns of one accumulator set (always two accumulators)
+    const int NI = p.n_issuers;                   // issuing threads: 2, or 4 (plain products with four blocks of K per stage)
+    const int acc_cols = NI * p.NB;               // tensor-memory columns of one accumulator set: an accumulator per issuer
     uint32_t ncols = 32;
     while ((int)ncols < 2 * acc_cols) ncols <<= 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             gm_mbar_init(full0 + s * 8, 1);
-            gm_mbar_init(empty0 + s * 8, 2);      // both issuers
+            gm_mbar_init(empty0 + s * 8, NI);     // every issuer
         }
         for (int a = 0; a < 2; ++a) {
-            gm_mbar_init(tfull0 + a * 8, 2);
+            gm_mbar_init(tfull0 + a * 8, NI);
             gm_mbar_init(tempty0 + a * 8, 4);     // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -141,41 +149,68 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_mid_kernel(const __grid_co
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            auto issue = [&](long long i, int stage, bool weights, bool acts) {
-                const int u = b + (int)(i / p.n_chunks) * G, c = (int)(i % p.n_chunks);
-                const int tile = u / p.n_bb, bb = u - tile * p.n_bb;
+            auto issue = [&](int tile, int bb, int c, int stage, bool weights, bool acts) {
                 const uint32_t full = full0 + stage * 8, dst = gm_smem(smem + stage * stage_bytes);
-                if (weights) {
-                    gm_mbar_expect_tx(full, (uint32_t)stage_bytes);
-                    for (int kb = 0; kb < KB; ++kb) {             // blocks past the end of K come in as zeros
-                        gm_tma_2d(dst + kb * a_bytes, &map_w, (c * KB + kb) * GM_BK, tile * GM_BM, full);
-                        if (n_a == 2) gm_tma_2d(dst + (KB + kb) * a_bytes, &map_w2, (c * KB + kb) * GM_BK, tile * GM_BM, full);
+                if (weights) gm_mbar_expect_tx(full, (uint32_t)stage_bytes);
+                if (p.tma3d) {
+                    // K a multiple of 64: the operands are seen as [K / 64][rows][64] and all the stage's blocks of K of an
+                    // operand come in one copy (a copy costs its issuing thread some 100 clocks)
+                    if (weights) {
+                        gm_tma_3d(dst, &map_w, 0, tile * GM_BM, c * KB, full);
+                        if (n_a == 2) gm_tma_3d(dst + KB * a_bytes, &map_w2, 0, tile * GM_BM, c * KB, full);
+                    }
+                    if (acts) gm_tma_3d(dst + KB * n_a * a_bytes, &map_x, 0, bb * p.NB, c * KB, full);
+                } else {
+                    if (weights) {
+                        for (int kb = 0; kb < KB; ++kb) {         // blocks past the end of K come in as zeros
+                            gm_tma_2d(dst + kb * a_bytes, &map_w, (c * KB + kb) * GM_BK, tile * GM_BM, full);
+                            if (n_a == 2) gm_tma_2d(dst + (KB + kb) * a_bytes, &map_w2, (c * KB + kb) * GM_BK, tile * GM_BM, full);
+                        }
+                    }
+                    if (acts) {
+                        for (int kb = 0; kb < KB; ++kb)
+                            gm_tma_2d(dst + KB * n_a * a_bytes + kb * b_bytes, &map_x, (c * KB + kb) * GM_BK, bb * p.NB, full);
                     }
                 }
-                if (acts) {
-                    for (int kb = 0; kb < KB; ++kb)
-                        gm_tma_2d(dst + KB * n_a * a_bytes + kb * b_bytes, &map_x, (c * KB + kb) * GM_BK, bb * p.NB, full);
-                }
             };
+            // (unit, chunk) pairs in order, without a division per pair: k counts this block's units, c the chunks of K
             const int n_early = (int)(total < STAGES ? total : STAGES);
-            for (int i = 0; i < n_early; ++i) issue(i, i, true, false);      // the ring is empty: no wait
+            {
+                int k = 0, c = 0;
+                for (int i = 0; i < n_early; ++i) {               // the ring is empty: no wait; weights only
+                    const int u = b + k * G, tile = u / p.n_bb;
+                    issue(tile, u - tile * p.n_bb, c, i, true, false);
+                    if (++c == p.n_chunks) { c = 0; ++k; }
+                }
+            }
             il_pdl_wait();                        // x comes from the kernel before
-            for (int i = 0; i < n_early; ++i) issue(i, i, false, true);
+            int k = 0, c = 0;
+            for (int i = 0; i < n_early; ++i) {
+                const int u = b + k * G, tile = u / p.n_bb;
+                issue(tile, u - tile * p.n_bb, c, i, false, true);
+                if (++c == p.n_chunks) { c = 0; ++k; }
+            }
             int stage = n_early == STAGES ? 0 : n_early;
             uint32_t phase = n_early == STAGES ? 1 : 0;
-            for (long long i = n_early; i < total; ++i) {
-                if (!gm_mbar_wait(empty0 + stage * 8, phase ^ 1)) { atomicExch(p.status, 51); break; }
-                issue(i, stage, true, true);
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            for (; k < n_my; ++k, c = 0) {
+                const int u = b + k * G, tile = u / p.n_bb, bb = u - tile * p.n_bb;
+                bool ok = true;
+                for (; c < p.n_chunks; ++c) {
+                    if (!gm_mbar_wait(empty0 + stage * 8, phase ^ 1)) { atomicExch(p.status, 51); ok = false; break; }
+                    issue(tile, bb, c, stage, true, true);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
             }
         }
-    } else if (warp == 1 || warp == 2) {
+    } else if (warp >= 1 && warp <= 4) {
         // ---------------- tensor-core issue: two threads, each with an accumulator of its own ----------------
-        // A unit always has two accumulators. SwiGLU: gate (issuer 0) and up (issuer 1). Plain: the 64-wide blocks of K
-        // taken in turn, even ones by issuer 0 and odd ones by issuer 1; the epilogue adds the two. One thread alone could
-        // not issue products fast enough for the memory's rate: a product of M = 64 covers 2 KB of weights and cost it some 80
-        // clocks, dependent as they are on one accumulator.
-        if (lane == 0) {
+        // Every issuer has an accumulator of its own. SwiGLU: gate (issuer 0) and up (issuer 1). Plain: the stage's 64-wide
+        // blocks of K dealt out in turn to two or four issuers; the epilogue adds their accumulators. One thread issues a
+        // product every 55 clocks at best (measured on fixed operands; 76 in this loop) and a product of M = 64 covers
+        // only 2 KB of weights, which is half of what the memory's rate needs; the tensor pipe itself takes some 25 clocks
+        // for such a product when several threads feed it.
+        if (lane == 0 && warp - 1 < NI) {
             const int me = warp - 1;
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NB >> 3) << 17) | ((uint32_t)(GM_BM >> 4) << 24);
             int stage = 0, acc = 0;
@@ -200,13 +235,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_mid_kernel(const __grid_co
                                 gm_mma(d_tmem, da0 + (uint64_t)(((me * KB + kb) * a_bytes >> 4) + kk * 2),
                                        db0 + (uint64_t)kb * b_step + (uint64_t)(kk * 2), idesc, (c > 0 || kb > 0 || kk > 0) ? 1u : 0u);
                     } else {
-#pragma unroll
-                        for (int kh = 0; kh < KB / 2; ++kh) {
-                            const int kb = 2 * kh + me;
+                        for (int kb = me; kb < KB; kb += NI) {        // this issuer's blocks of K
 #pragma unroll
                             for (int kk = 0; kk < GM_BK / 16; ++kk)
                                 gm_mma(d_tmem, da0 + (uint64_t)((kb * a_bytes >> 4) + kk * 2), db0 + (uint64_t)kb * b_step + (uint64_t)(kk * 2),
-                                       idesc, (c > 0 || kh > 0 || kk > 0) ? 1u : 0u);
+                                       idesc, (c > 0 || kb > me || kk > 0) ? 1u : 0u);
                         }
                     }
                     gm_commit(empty0 + stage * 8);            // the stage is free once both issuers' products have read it
@@ -217,11 +250,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_mid_kernel(const __grid_co
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
-    } else {
+    } else if (warp >= 5) {
         // ---------------- epilogue: warp w reads tensor-memory lanes 32 * (w % 4) .. + 31, of which the first 16 hold
         // rows 16 * (w % 4) .. + 15 of the tile ----------------
         il_pdl_wait();                            // these warps write the output
-        const int q = warp & 3;
+        const int q = warp & 3;                   // warps 5..8
         const bool live = BM == 128 || lane < 16;
         const int row = BM == 128 ? q * 32 + lane : q * 16 + lane;    // this thread's W row within the tile (M = 64: lanes 16..31 have none)
         int acc = 0;
@@ -241,13 +274,23 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_mid_kernel(const __grid_co
                 gm_ld16(taddr + p.NB + j0, vu);
                 asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
                 float y[16];
+                if (p.mode == GM_GLU) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (p.mode == GM_GLU) {
+                    for (int j = 0; j < 16; ++j)
                         y[j] = il_silu_mul_fast(__fmaf_rn(p.alpha, __uint_as_float(vg[j]), bg), __fmaf_rn(p.alpha, __uint_as_float(vu[j]), bu));
-                    } else {                      // the even and the odd blocks of K
-                        y[j] = __fmaf_rn(p.alpha, __uint_as_float(vg[j]) + __uint_as_float(vu[j]), bg);
+                } else {                          // the issuers' shares of K, added in the order of the issuers
+                    float sum[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sum[j] = __uint_as_float(vg[j]) + __uint_as_float(vu[j]);
+                    if (NI == 4) {
+                        gm_ld16(taddr + 2 * p.NB + j0, vg);
+                        gm_ld16(taddr + 3 * p.NB + j0, vu);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) sum[j] = (sum[j] + __uint_as_float(vg[j])) + __uint_as_float(vu[j]);
                     }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) y[j] = __fmaf_rn(p.alpha, sum[j], bg);
                 }
                 if (n_ok) {
                     if (p.out_kind == IL_F32) {
@@ -307,6 +350,21 @@ static int gm_make_map(CUtensorMap* map, const void* base, int rows, int K, int 
     return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
 }
 
+// The same matrix as [K / 64][rows][64] (K a multiple of 64), read in boxes of [kblk][box_rows][64]: kblk blocks of K at once,
+// each landing as a [box_rows x 64] tile with the 128-byte swizzle.
+static int gm_make_map3(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows, int kblk) {
+    gm_encode_fn enc = gm_encoder();
+    if (!enc) return IL_UNSUPPORTED;
+    cuuint64_t dims[3] = {(cuuint64_t)GM_BK, (cuuint64_t)rows, (cuuint64_t)(K / GM_BK)};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)GM_BK * 2};
+    cuuint32_t box[3] = {(cuuint32_t)GM_BK, (cuuint32_t)box_rows, (cuuint32_t)kblk};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
+}
+
 static int gm_sm_count() {
     static int n[64];
     int dev = 0;
@@ -357,17 +415,6 @@ IL_EXPORT int il_gemm_mid(const void* x, int ldx, const void* W, int ldw, void* 
     p.n_units = p.n_tiles * p.n_bb;
     p.ldo = ldo; p.out_kind = out_kind; p.alpha = alpha; p.bias = bias; p.out = out; p.status = status;
 
-    CUtensorMap map_w, map_w2, map_x;
-    int rc = gm_make_map(&map_w, W, N, K, ldw, bm);
-    if (rc) return rc;
-    map_w2 = map_w;
-    if (glu) {
-        rc = gm_make_map(&map_w2, (const __nv_bfloat16*)W + (size_t)N * ldw, N, K, ldw, bm);
-        if (rc) return rc;
-    }
-    rc = gm_make_map(&map_x, x, M, K, ldx, p.NB);
-    if (rc) return rc;
-
     const int a_bytes = bm * GM_BK * 2, b_bytes = p.NB * GM_BK * 2;
     const int tail = (2 * GM_MAX_STAGES + 4) * 8 + 16;
     int kblk = GM_KBLK, stage_bytes = 0, n_stages = 0;
@@ -380,7 +427,29 @@ IL_EXPORT int il_gemm_mid(const void* x, int ldx, const void* W, int ldw, void* 
     if (n_stages < 2) return IL_UNSUPPORTED;
     p.n_stages = n_stages;
     p.kblk = kblk;
+    p.n_issuers = (!glu && kblk == 4 && p.NB <= 64) ? 4 : 2;      // (four accumulators of NB columns, twice, must fit 512 columns)
     p.n_chunks = (K + GM_BK * kblk - 1) / (GM_BK * kblk);
+    p.tma3d = (K % GM_BK == 0) ? 1 : 0;
+
+    CUtensorMap map_w, map_w2, map_x;
+    int rc;
+    if (p.tma3d) {
+        rc = gm_make_map3(&map_w, W, N, K, ldw, bm, kblk);
+        if (rc) return rc;
+        map_w2 = map_w;
+        if (glu) rc = gm_make_map3(&map_w2, (const __nv_bfloat16*)W + (size_t)N * ldw, N, K, ldw, bm, kblk);
+        if (rc) return rc;
+        rc = gm_make_map3(&map_x, x, M, K, ldx, p.NB, kblk);
+        if (rc) return rc;
+    } else {
+        rc = gm_make_map(&map_w, W, N, K, ldw, bm);
+        if (rc) return rc;
+        map_w2 = map_w;
+        if (glu) rc = gm_make_map(&map_w2, (const __nv_bfloat16*)W + (size_t)N * ldw, N, K, ldw, bm);
+        if (rc) return rc;
+        rc = gm_make_map(&map_x, x, M, K, ldx, p.NB);
+        if (rc) return rc;
+    }
     const int smem = 1024 + n_stages * stage_bytes + tail;
     const int grid = p.n_units < n_sm ? p.n_units : n_sm;
     auto launch = [&](auto kernel) -> int {
