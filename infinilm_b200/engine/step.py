@@ -46,9 +46,14 @@ class Workspace:
     def __init__(self, device, max_tokens: int):
         self.device, self.max_tokens = device, int(max_tokens)
         self._bufs: Dict[tuple, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}      # the first n rows of a buffer, made once per n (a step asks
         self.version = 0                          # bumped when a buffer is replaced (captured graphs go stale)
 
     def rows(self, tag: str, n: int, width: int, dtype: torch.dtype) -> torch.Tensor:
+        vkey = (tag, n, width, dtype)             # for the same few dozen views layer after layer)
+        view = self._views.get(vkey)
+        if view is not None:
+            return view
         key = (tag, width, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.shape[0] < n:
@@ -60,7 +65,11 @@ class Workspace:
                 self.version += 1
             buf = torch.empty((cap, width), dtype=dtype, device=self.device)
             self._bufs[key] = buf
-        return buf[:n]
+            self._views = {k: v for k, v in self._views.items() if k[0] != tag}
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = self._views[vkey] = buf[:n]
+        return view
 
     def flat(self, tag: str, n: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """`zero`: the buffer is zero when it is made (its users leave it zero)."""
@@ -96,9 +105,22 @@ class StepContext:
     tap: Optional[Callable] = None                # debug hook: tap(name, resid, pending)
     lengths_are_bounds: bool = False              # h_qlen / h_kvlen are upper bounds (a step replayed as a graph)
 
+    def prompt_tiles(self, tokens_per_tile: int) -> int:
+        """How many tiles of `tokens_per_tile` tokens the prompt portions (the entries behind the first n_decode) are cut
+        into, each portion by itself: the exact number, or - when lengths are bounds - the most that any split of the
+        portions' tokens can give, so that a kernel launched per tile gets the same grid whenever the step is replayed."""
+        if not self.lengths_are_bounds:
+            return sum((q + tokens_per_tile - 1) // tokens_per_tile for q in self.h_qlen[self.n_decode:])
+        n_portions = self.n_entries - self.n_decode
+        if n_portions <= 0:
+            return 0
+        return (self.T - self.n_decode + tokens_per_tile - 1) // tokens_per_tile + n_portions - 1
+
 
 class StepRunner:
     """Owns the model, the cache manager and the device buffers, and runs steps."""
+    GRAPH_AFTER = 2                               # a step with prompt portions is captured when its key comes a third time
+    MAX_GRAPHS = 128                              # captured steps kept
 
     def __init__(self, model: CausalLM, cache: CacheManager, device, max_batch_tokens: int):
         self.model, self.cache, self.device = model, cache, torch.device(device)
@@ -109,9 +131,13 @@ class StepRunner:
         self.tap: Optional[Callable] = None
         self.use_graphs = False
         self._graphs: Dict[tuple, "_GraphSlot"] = {}
+        self._graph_pool = None
+        self.graph_prompts = True                 # steps with prompt portions are replayed too, once their key has come back
+        self._shapes_seen: Dict[tuple, int] = {}
         self.h2d_bytes = 0
         self.steps_run = 0
         self.tokens_run = 0
+        self.portion_replays = 0                  # steps with prompt portions that were replayed as graphs
         self._last_decode: Optional["_DecodeBatch"] = None    # the replayed decode step just run, if the next may follow it
         self.fast_steps = 0
 
@@ -283,18 +309,36 @@ class StepRunner:
         tbl_ptr = np.array([[s_.tables[g].address() for s_ in seqs] for g in paged], dtype=np.uint64).reshape(len(paged), E)
         widths = {g: max(1, int(tbl_len[k].max())) for k, g in enumerate(paged)}
 
-        # A decode-only step that wants every row can be replayed as a CUDA graph: the batch is
-        # padded to a bucket of entries and of block-table width, so that the captured launches
-        # and the addresses they read stay the same from step to step.
+        # A step can be replayed as a CUDA graph when its launches and the addresses they read depend on nothing but a
+        # key. A decode-only step that wants every row: the batch is padded to a bucket of entries and of block-table
+        # width. A step with prompt portions, each entry wanting at most one row: the single tokens are padded to a
+        # bucket, the number of portions and of their tokens is part of the key (kernels that are launched per tile of
+        # a portion are given a bound on the tiles that the key fixes), and the key must have been seen before - a
+        # serving run that cuts long prompts into equal portions repeats it, arbitrary mixes do not.
         graph_key = None
-        Ep, Tp = E, T
-        if (self.use_graphs and self.tap is None and n_decode == E and self.model.graph_safe
-                and int(n_want_of.min()) == 1 and int(n_want_of.max()) == 1):
-            Ep = _bucket(E, _ENTRY_BUCKETS)
-            widths = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
-            Tp = Ep
-            graph_key = (Ep, tuple(sorted(widths.items())))
-        n_want = Ep if graph_key is not None else int(want_off[E])
+        Ep, Tp, pad_at, n_want_fixed = E, T, E, -1
+        if self.use_graphs and self.tap is None and self.model.graph_safe:
+            single_want = n_want_of[n_tok == 1]
+            if n_decode == E and int(n_want_of.min()) == 1 and int(n_want_of.max()) == 1:
+                Ep = _bucket(E, _ENTRY_BUCKETS)
+                widths = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
+                Tp = Ep
+                graph_key = (Ep, tuple(sorted(widths.items())))
+            elif (self.graph_prompts and int(n_want_of.max()) <= 1 and (single_want.size == 0 or int(single_want.min()) == 1)):
+                Dp = _bucket(n_decode, _ENTRY_BUCKETS) if n_decode else 0
+                bw = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
+                key = ("portions", Dp, E - n_decode, T - n_decode, tuple(sorted(bw.items())))
+                seen = self._shapes_seen.get(key, 0)
+                if seen < self.GRAPH_AFTER:
+                    if len(self._shapes_seen) > 4096:
+                        self._shapes_seen.clear()
+                    self._shapes_seen[key] = seen + 1
+                else:
+                    graph_key, widths = key, bw
+                    Ep, Tp = Dp + E - n_decode, Dp + T - n_decode
+            if graph_key is not None:
+                pad_at, n_want_fixed = n_decode, Ep
+        n_want = n_want_fixed if graph_key is not None else int(want_off[E])
         n_neg = int((tokens < 0).sum())
         n_patch = Tp if graph_key is not None else n_neg          # a replayed step's buffer is sized once, for any number
         n_ints = (3 * Tp + (Ep + 1) + Ep + max(n_want, 1) + 2 * Ep + sum(Ep * w for w in widths.values()) + 2 * n_patch)
@@ -302,7 +346,13 @@ class StepRunner:
         if graph_key is not None:
             gs = self._graphs.get(graph_key)
             if gs is None:
-                gs = self._graphs[graph_key] = _GraphSlot(torch.empty(n_ints, dtype=torch.int32, device=self.device))
+                if len(self._graphs) >= self.MAX_GRAPHS:          # the key used longest ago makes room
+                    torch.cuda.current_stream(self.device).synchronize()
+                    del self._graphs[next(iter(self._graphs))]
+                gs = _GraphSlot(torch.empty(n_ints, dtype=torch.int32, device=self.device))
+            else:
+                del self._graphs[graph_key]
+            self._graphs[graph_key] = gs          # (a dict keeps the order of insertion: the last used key is last)
             dev = gs.desc
         h = host.numpy()
         # ---- the descriptors, filled by native code (csrc/step_fill.cpp) --------------------------------------------
@@ -313,13 +363,14 @@ class StepRunner:
         offs = np.zeros(12, dtype=np.int32)
         outs = np.zeros(3, dtype=np.int32)          # patches, wanted rows, entry at fault
         rc = ops.step_fill(h, host.numel(), E, Ep, Tp, order, n_tok, start, slots, fresh, tokens, tok_off, w_arr, tbl_ptr, tbl_len,
-                           scratch, self.cache.slots.n_slots, want, want_off, graph_key is not None, n_patch, offs, outs)
+                           scratch, self.cache.slots.n_slots, want, want_off, pad_at, n_want_fixed, n_patch, offs, outs)
         if rc != 0:
             i = int(outs[2])
             who = f"entry {i} ({seqs[i].seq_id!r})" if i >= 0 else "the step"
             raise StepError({-11: f"{who}: a wanted place is outside its {int(n_tok[i]) if i >= 0 else 0} tokens",
                              -12: f"{who}: its block table is wider than the step's", -13: "the step's descriptors outgrew their buffer",
-                             -14: f"{who}: more device tokens than the step has room for"}.get(rc, f"step_fill failed ({rc})"))
+                             -14: f"{who}: more device tokens than the step has room for",
+                             -15: "the step's counts do not fit together"}.get(rc, f"step_fill failed ({rc})"))
         n_patches = int(outs[0])
         o = offs.tolist()
         off = o[11]
@@ -331,8 +382,11 @@ class StepRunner:
             s_bt[g] = (a_, a_ + Ep * widths[g])
             a_ += Ep * widths[g]
         s_prow, s_psrc = (o[9], o[9] + n_patch), (o[10], o[10] + n_patch)
-        h_qlen = n_tok[order].tolist() + [1] * (Ep - E)
-        h_kvlen = (start + n_tok)[order].tolist() + [1] * (Ep - E)
+        n_pad = Ep - E
+        h_qlen = n_tok[order].tolist()
+        h_kvlen = (start + n_tok)[order].tolist()
+        h_qlen[n_decode:n_decode] = [1] * n_pad
+        h_kvlen[n_decode:n_decode] = [1] * n_pad
         dev[:off].copy_(host[:off], non_blocking=True)
         if n_patches:                             # tokens the host has not seen: copied in on the device
             ops.patch_tokens(dev[s_tok[0]: s_tok[1]], dev[s_prow[0]: s_prow[0] + n_patches],
@@ -344,11 +398,13 @@ class StepRunner:
 
         def view(s):
             return dev[s[0]: s[1]]
-        if graph_key is not None:                 # launch plans must not depend on this step's lengths
+        n_single = n_decode + n_pad
+        if graph_key is not None:                 # launch plans must not depend on this step's lengths, only on the key
             bound = min(widths[g] for g in paged) * kpage if paged else 1
-            h_kvlen, h_qlen = [bound] * Ep, [1] * Ep
+            h_kvlen = [bound] * Ep
+            h_qlen = [1] * n_single + [Tp - n_single] * (Ep - n_single)
         ctx = StepContext(
-            dtype=self.dtype, T=Tp, n_entries=Ep, n_decode=Ep if graph_key is not None else n_decode,
+            dtype=self.dtype, T=Tp, n_entries=Ep, n_decode=n_single,
             token_ids=view(s_tok), tok_pos=view(s_pos), tok_entry=view(s_ent), entry_qstart=view(s_qs),
             entry_kvlen=view(s_kv), want_rows=dev[s_want[0]: s_want[0] + n_want], n_want=n_want, ws=self.ws,
             h_qlen=h_qlen, h_kvlen=h_kvlen, max_qlen=max(h_qlen), max_kvlen=max(h_kvlen), tap=self.tap,
@@ -382,7 +438,9 @@ class StepRunner:
                 else:
                     n0 = ops.launch_count()
                     g_ = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g_):
+                    if self._graph_pool is None:  # one pool for all graphs: they never run at the same time
+                        self._graph_pool = torch.cuda.graph_pool_handle()
+                    with torch.cuda.graph(g_, pool=self._graph_pool):
                         gs.logits = self.model.forward(ctx, caches)
                     gs.n_kernels = ops.launch_count() - n0
                     ops.count_launches(-gs.n_kernels)    # capturing launches nothing
@@ -391,13 +449,13 @@ class StepRunner:
             if gs.graph is not None:
                 gs.graph.replay()
                 ops.count_launches(gs.n_kernels)
-                if not any(grp.need.kind == "paged_kv" and grp.need.window is not None for grp in groups):
+                self.portion_replays += n_decode != E
+                if n_decode == E and not any(grp.need.kind == "paged_kv" and grp.need.window is not None for grp in groups):
                     # the next step may be the same requests with one more token each: keep what it can start from
                     self._last_decode = _DecodeBatch(
                         seqs=seqs, gs=gs, E=E, Ep=Ep, widths=dict(widths), mirror=h[:off].copy(), lens=start + 1,
                         spans=dict(tok=s_tok, pos=s_pos, kv=s_kv, rs=s_rs, wsl=s_wsl, bt=dict(s_bt), prow=s_prow, psrc=s_psrc), n_ints=off)
-            logits = gs.logits
-            logits = logits[:E]                   # (all entries bring one token: the running order is the caller's)
+            logits = gs.logits[:int(want_off[E])]         # the rows asked for come first, in the caller's order
         for s_, n_ in zip(seqs, new_len):
             self.cache.commit(s_, n_)
         self.steps_run += 1

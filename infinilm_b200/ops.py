@@ -36,8 +36,13 @@ def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
     return _c_void_p(t.data_ptr())
 
 
+_raw_stream = torch._C._cuda_getCurrentRawStream
+_cur_device = torch._C._cuda_getDevice
+
+
 def _stream() -> _c_void_p:
-    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current device's current stream (asked of the runtime directly: this runs once per launch)."""
+    return _c_void_p(_raw_stream(_cur_device()))
 
 
 def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
@@ -79,17 +84,20 @@ def _check(code: int, what: str) -> None:
     raise KernelError(f"{what}: error {code}")
 
 
-_sigs_done = set()
+_fns = {}
 
 
 def _fn(lib_name: str, fn_name: str, argtypes, defines=None):
-    lib = build.load(lib_name, defines)
-    f = getattr(lib, fn_name)
-    key = (id(lib), fn_name)
-    if key not in _sigs_done:
+    """The entry point `fn_name` of the library built from `lib_name` with `defines`; looked up once."""
+    key = (lib_name, fn_name, next(iter(defines.values())) if defines else None)
+    f = _fns.get(key)
+    if f is None:
+        if defines and len(defines) != 1:
+            raise KernelError("a kernel library is keyed by one definition")
+        f = getattr(build.load(lib_name, defines), fn_name)
         f.argtypes = argtypes
         f.restype = _c_int
-        _sigs_done.add(key)
+        _fns[key] = f
     return f
 
 
@@ -359,7 +367,18 @@ def prefill_tc5_ok(head_dim: int, group: int, page_size: int, kv_map: Optional[t
     needs the third map of `kv_tensor_map`, a page's K or V as tensor-core tiles)."""
     if not (head_dim in (64, 128) and 0 < group <= 128 and page_size == 16):
         return False
-    return kv_map is None or (kv_map.numel() == KV_MAP_BYTES and bool(kv_map[256:].any()))
+    return kv_map is None or _has_third_map(kv_map)
+
+
+def _has_third_map(kv_map: torch.Tensor) -> bool:
+    """Whether this host tensor is a `kv_tensor_map` result with its third map filled; looked at once per tensor
+    object (the answer is kept on the object, so another tensor at the same address is looked at again)."""
+    ok = getattr(kv_map, "_il_third_map", None)
+    if ok is None:
+        ok = (not kv_map.is_cuda and kv_map.dtype == torch.uint8 and kv_map.numel() == KV_MAP_BYTES
+              and bool(kv_map[256:].any()))
+        kv_map._il_third_map = ok
+    return ok
 
 
 def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Tensor, block_table: torch.Tensor,
@@ -371,7 +390,7 @@ def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Te
     _need_cuda(qkv, out, block_table, entry_qstart, entry_kvlen)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc5: bfloat16 tensors")
-    if kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != KV_MAP_BYTES or not bool(kv_map[256:].any()):
+    if not _has_third_map(kv_map):
         raise KernelError("attention_prefill_tc5: kv_map must be the host tensor kv_tensor_map returned, with its third map")
     if out.shape != (qkv.shape[0], n_heads * head_dim):
         raise KernelError("attention_prefill_tc5: out [T, heads*head_dim]")
@@ -609,10 +628,12 @@ def _np_ptr(a) -> _c_void_p:
 
 
 def step_fill(out, out_cap: int, E: int, Ep: int, Tp: int, order, n_tok, start, slot, fresh, tokens, tok_off, widths, tbl_ptr,
-              tbl_len, scratch_page, scratch_slot: int, want, want_off, graph_mode: bool, n_patch_cap: int, offsets, outs) -> int:
+              tbl_len, scratch_page, scratch_slot: int, want, want_off, pad_at: int, n_want_fixed: int, n_patch_cap: int, offsets,
+              outs) -> int:
     """Native host code (csrc/step_fill.cpp): fills a step's descriptors into the int32 host array `out` from columns
     given as numpy arrays (int32 unless said: `fresh` uint8, `tokens` int64, `tbl_ptr` uint64 addresses of the block
-    tables' arrays). `offsets` (int32 [12]) receives where each part starts, `outs` (int32 [3]) the number of device
+    tables' arrays). The Ep - E padding entries of a step that is replayed as a graph run behind the first `pad_at`
+    entries; `n_want_fixed` is such a step's number of wanted rows (-1: as many as are asked for). `offsets` (int32 [12]) receives where each part starts, `outs` (int32 [3]) the number of device
     tokens, of wanted rows, and the entry at fault. Returns 0 or the negative code of the fault."""
     for name, a, dt in (("order", order, "int32"), ("n_tok", n_tok, "int32"), ("start", start, "int32"), ("slot", slot, "int32"),
                         ("fresh", fresh, "uint8"), ("tokens", tokens, "int64"), ("tok_off", tok_off, "int32"),
@@ -629,11 +650,11 @@ def step_fill(out, out_cap: int, E: int, Ep: int, Tp: int, order, n_tok, start, 
     f = lib.il_step_fill
     if not getattr(f, "_sig", False):
         f.argtypes = ([_c_void_p, ctypes.c_longlong, _c_int, _c_int, _c_int] + [_c_void_p] * 7 + [_c_int] + [_c_void_p] * 4 + [_c_int]
-                      + [_c_void_p] * 2 + [_c_int, _c_int] + [_c_void_p] * 4)
+                      + [_c_void_p] * 2 + [_c_int, _c_int, _c_int] + [_c_void_p] * 4)
         f.restype = _c_int
         f._sig = True
     return int(f(_np_ptr(out), out_cap, E, Ep, Tp, _np_ptr(order), _np_ptr(n_tok), _np_ptr(start), _np_ptr(slot), _np_ptr(fresh),
                  _np_ptr(tokens), _np_ptr(tok_off), int(widths.size), _np_ptr(widths), _np_ptr(tbl_ptr), _np_ptr(tbl_len),
-                 _np_ptr(scratch_page), scratch_slot, _np_ptr(want), _np_ptr(want_off), int(graph_mode), n_patch_cap,
+                 _np_ptr(scratch_page), scratch_slot, _np_ptr(want), _np_ptr(want_off), int(pad_at), int(n_want_fixed), n_patch_cap,
                  _c_void_p(offsets.ctypes.data), _c_void_p(outs.ctypes.data), _c_void_p(outs.ctypes.data + 4),
                  _c_void_p(outs.ctypes.data + 8)))

@@ -155,7 +155,7 @@ class Attention(Mixer):
             tc5 = (self.prefill_kernel != "mma" and cache.tma_map is not None
                    and ops.prefill_tc5_ok(self.hd, G, cache.page_size, cache.tma_map))
             tpt = max(1, (ops.prefill_tc5_rows(self.hd) if tc5 else 64) // G)
-            n_tiles = sum((q + tpt - 1) // tpt for q in ctx.h_qlen[n_dec:])
+            n_tiles = ctx.prompt_tiles(tpt)
             if tc5:
                 ops.attention_prefill_tc5(qkv, out, cache.tma_map, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
                                           n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,

@@ -35,6 +35,7 @@ class Linear:
         if tuple(weight.shape) != (self.out_features, self.in_features):
             raise ValueError(f"linear weight {tuple(weight.shape)} != {(self.out_features, self.in_features)}")
         self.weight = weight.to(self.dtype).contiguous()
+        self._weight_t = self.weight.t()          # the view the library product takes, made once
         if bias is not None:
             self.bias = bias.to(torch.float32).contiguous()
 
@@ -59,13 +60,13 @@ class Linear:
             return out
         # Library matrix product (cuBLAS through torch), f32 accumulation inside.
         if out_f32:
-            torch.mm(x, self.weight.t(), out_dtype=torch.float32, out=out)
+            torch.mm(x, self._weight_t, out_dtype=torch.float32, out=out)
             if self.alpha != 1.0:
                 out.mul_(self.alpha)
         elif self.alpha != 1.0:
-            torch.addmm(out, x, self.weight.t(), beta=0.0, alpha=self.alpha, out=out)
+            torch.addmm(out, x, self._weight_t, beta=0.0, alpha=self.alpha, out=out)
         else:
-            torch.mm(x, self.weight.t(), out=out)
+            torch.mm(x, self._weight_t, out=out)
         if self.bias is not None:
             ops.add_bias(out, self.bias)
         return out

@@ -12,13 +12,15 @@ from infinilm_b200.cache.manager import PageTable
 
 def _case(rng):
     E, sub = rng.randint(1, 9), rng.choice([1, 2, 16])
-    graph = rng.random() < 0.3
-    n_tok = np.array([1 if graph or rng.random() < 0.5 else rng.randint(2, 7) for _ in range(E)], dtype=np.int32)
+    graph = rng.random() < 0.4                    # a step laid out for replay: padding entries, a fixed number of wanted rows
+    only_single = graph and rng.random() < 0.5
+    n_tok = np.array([1 if only_single or rng.random() < 0.5 else rng.randint(2, 7) for _ in range(E)], dtype=np.int32)
     start = np.array([rng.randint(0, 40) for _ in range(E)], dtype=np.int32)
     slot = np.array(rng.sample(range(1, 20), E), dtype=np.int32)
     fresh = np.array([rng.random() < 0.3 for _ in range(E)], dtype=np.uint8)
     toks = [[rng.choice([rng.randint(0, 99), -1 - rng.randint(0, 5)]) for _ in range(n)] for n in n_tok]
-    wants = [[0] if graph else sorted(rng.sample(range(n), rng.randint(0, n))) for n in n_tok]
+    wants = [([0] if n == 1 else rng.choice([[], [rng.randrange(n)]])) if graph else sorted(rng.sample(range(n), rng.randint(0, n)))
+             for n in n_tok]
     tables = []
     for i in range(E):
         t = PageTable(sub=sub)
@@ -35,8 +37,10 @@ def test_native_filler_equals_a_plain_construction(seed):
         E, sub, graph, n_tok, start, slot, fresh, toks, wants, tables = _case(rng)
         order = np.argsort(n_tok != 1, kind="stable").astype(np.int32)
         T = int(n_tok.sum())
-        Ep = E + (rng.randint(0, 3) if graph else 0)
-        Tp = Ep if graph else T
+        n_pad = rng.randint(0, 3) if graph else 0
+        Ep, Tp = E + n_pad, T + n_pad
+        n_single = int((n_tok == 1).sum())        # the padding entries run behind the single tokens
+        n_want_fixed = Ep if graph else -1
         tokens = np.array([t for row in toks for t in row], dtype=np.int64)
         tok_off = np.zeros(E + 1, np.int32)
         np.cumsum(n_tok, out=tok_off[1:])
@@ -50,11 +54,17 @@ def test_native_filler_equals_a_plain_construction(seed):
         out = np.full(40000, 777, dtype=np.int32)
         offs, outs = np.zeros(12, np.int32), np.zeros(3, np.int32)
         rc = ops.step_fill(out, out.size, E, Ep, Tp, order, n_tok, start, slot, fresh, tokens, tok_off, np.array([W], np.int32), tbl_ptr,
-                           tbl_len, np.array([99 * sub], np.int32), 31, want, want_off, graph, n_patch, offs, outs)
+                           tbl_len, np.array([99 * sub], np.int32), 31, want, want_off, n_single, n_want_fixed, n_patch, offs, outs)
         assert rc == 0
         o = offs.tolist()
         qs, tok, pos, ent, kv, rs, ws, bt, pr, ps, first_row = [0], [], [], [], [], [], [], [], [], [], {}
-        for k, i in enumerate(order.tolist()):
+        running = order.tolist()
+        running = running[:n_single] + [None] * n_pad + running[n_single:]
+        for k, i in enumerate(running):
+            if i is None:                         # a padding entry of a replayed step
+                tok.append(0), pos.append(0), ent.append(k), qs.append(qs[-1] + 1), kv.append(1), rs.append(0), ws.append(31)
+                bt.append([99 * sub] + [-1] * (W - 1))
+                continue
             first_row[i] = qs[-1]
             for j, t in enumerate(toks[i]):
                 if t < 0:
@@ -69,10 +79,9 @@ def test_native_filler_equals_a_plain_construction(seed):
             ws.append(int(slot[i]))
             row = tables[i].array().tolist()
             bt.append(row + [-1] * (W - len(row)))
-        for k in range(E, Ep):                    # padding rows of a replayed step
-            tok.append(0), pos.append(0), ent.append(k), qs.append(qs[-1] + 1), kv.append(1), rs.append(0), ws.append(31)
-            bt.append([99 * sub] + [-1] * (W - 1))
-        wr = list(range(Ep)) if graph else [first_row[i] + w for i in range(E) for w in wants[i]]
+        wr = [first_row[i] + w for i in range(E) for w in wants[i]]
+        if graph:
+            wr += [0] * (Ep - len(wr))
         assert out[o[0]:o[0] + Tp].tolist() == tok and out[o[1]:o[1] + Tp].tolist() == pos and out[o[2]:o[2] + Tp].tolist() == ent
         assert out[o[3]:o[3] + Ep + 1].tolist() == qs and out[o[4]:o[4] + Ep].tolist() == kv
         assert out[o[5]:o[5] + len(wr)].tolist() == wr and outs[1] == len(wr)
@@ -98,7 +107,7 @@ def test_native_filler_reports_what_is_wrong():
             a["tokens"] = np.array(tokens, np.int64)
         return ops.step_fill(out, cap, 1, 1, 3, a["order"], a["n_tok"], a["start"], a["slot"], a["fresh"], a["tokens"], a["tok_off"],
                              np.array(widths, np.int32), tbl_ptr, tbl_len, np.array([9], np.int32), 7, np.array(want, np.int32),
-                             np.array([0, len(want)], np.int32), False, n_patch, offs, outs)
+                             np.array([0, len(want)], np.int32), 0, -1, n_patch, offs, outs)
     assert fill([0, 2]) == 0
     assert fill([3]) == -11 and outs[2] == 0         # a wanted place outside the entry's tokens
     assert fill([0], widths=(1,)) == -12 and outs[2] == 0
@@ -107,4 +116,4 @@ def test_native_filler_reports_what_is_wrong():
     with pytest.raises(ops.KernelError):
         ops.step_fill(out.astype(np.int64), 200, 1, 1, 3, one["order"], one["n_tok"], one["start"], one["slot"], one["fresh"], one["tokens"],
                       one["tok_off"], np.array([2], np.int32), tbl_ptr, tbl_len, np.array([9], np.int32), 7, np.array([0], np.int32),
-                      np.array([0, 1], np.int32), False, 0, offs, outs)
+                      np.array([0, 1], np.int32), 0, -1, 0, offs, outs)
