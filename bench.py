@@ -161,6 +161,51 @@ def profile_step(args) -> int:
     return 0
 
 
+def timeline_step(args) -> int:
+    """The kernels of one replayed decode step (batch --batch, --prompt-len tokens cached, --layers layers) with their start
+    and duration as the profiler of the framework underneath (CUPTI activity records) sees them inside the replayed
+    graph: kernels overlap their predecessors there, which a serialising profiler cannot show. Prints a table; nothing
+    here is a benchmark value."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from infinilm_b200.config import config_from_json
+    from infinilm_b200.engine import Engine, StepEntry
+    from infinilm_b200.weights import random_tensors
+    raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)
+    raw["num_hidden_layers"] = args.layers or 4
+    cfg = config_from_json(raw)
+    B, P = args.batch, args.prompt_len
+    eng = Engine.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", page_size=PAGE,
+                              num_pages=B * (P // PAGE + 4) + 8, max_seqs=max(B, 2), max_batch_tokens=4096)
+    eng.enable_graphs()
+    g = torch.Generator().manual_seed(1)
+    seqs = [eng.open(i) for i in range(B)]
+    for s in seqs:
+        ids = torch.randint(0, cfg.vocab_size, (P,), generator=g).tolist()
+        for a in range(0, P, PROMPT_LEN):
+            eng.step([StepEntry(s, ids[a:a + PROMPT_LEN], [])])
+    for _ in range(6):
+        eng.step([StepEntry(s, [5], [0]) for s in seqs])
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            eng.step([StepEntry(s, [5], [0]) for s in seqs])
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "emcpy" not in e.name and "emset" not in e.name),
+                key=lambda e: e.time_range.start)
+    last = ev[-(len(ev) // 3):]
+    t0 = last[0].time_range.start
+    print("| start us | duration us | start of the next - start us | kernel |")
+    print("|---|---|---|---|")
+    for e, nxt in zip(last, last[1:] + [None]):
+        a = e.time_range.start - t0
+        gap = f"{nxt.time_range.start - e.time_range.start:.1f}" if nxt is not None else ""
+        print(f"| {a:.1f} | {e.time_range.end - e.time_range.start:.1f} | {gap} | {e.name[:64]} |")
+    print(f"\nstep: {last[-1].time_range.end - t0:.1f} us, {len(last)} kernels, {raw['num_hidden_layers']} layers, batch {B}, {P} tokens cached")
+    return 0
+
+
 CONFIG_05B = dict(CONFIG_8B, num_hidden_layers=24, hidden_size=1024, num_attention_heads=16, num_key_value_heads=2, head_dim=64,
                   intermediate_size=4096, tie_word_embeddings=True,
                   rope_scaling={"rope_type": "longrope", "short_factor": [1.0 + 0.05 * i for i in range(32)],
@@ -242,6 +287,9 @@ def main() -> int:
     ap.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
                     help="run one step of this kind between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off); "
                          "use with --layers 2 to keep the capture small")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the kernels of one replayed decode step with start and duration inside the graph "
+                         "(--batch, --layers, --sizes, --prompt-len apply) and exit")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -265,6 +313,8 @@ def main() -> int:
 
     if args.profile_step:
         return profile_step(args)
+    if args.timeline:
+        return timeline_step(args)
     if args.workload != "default":
         return run_workload(args)
     raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)

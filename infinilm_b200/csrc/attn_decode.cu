@@ -59,19 +59,35 @@ __device__ __forceinline__ uint32_t ad_swz(uint32_t block, int r, int ch) {
 
 constexpr int AD_MAX_SPLITS = 128;
 
-// One warp merges the splits of one (token, head) row. Every load is issued before anything waits for one: the
-// (maximum, sum) pairs of all splits in one pass (lanes over splits), then the partial outputs sixteen splits at a
-// time, each lane four columns. The split factors exp2(m_s - M) go through `fs` (shared memory, AD_MAX_SPLITS floats
-// of this warp). A chain of dependent loads, one split after the other, is what this merge would otherwise cost.
-__device__ __forceinline__ void ad_merge_row(float* fs, const float* o_part, const float* ml_part,
-                                             size_t row, int n_valid, int n_splits, __nv_bfloat16* __restrict__ out, int lane) {
+// WPR warps merge the splits of one (token, head) row; warp `sub` of them takes splits sub, sub + WPR, ... Every load is
+// issued before anything waits for one: the partial outputs of the warp's first sixteen splits (each lane four columns),
+// then the (maximum, sum) pairs of all splits in one pass (lanes over splits), and only then the arithmetic. The split
+// factors exp2(m_s - M) go through `fs` (shared memory, AD_MAX_SPLITS floats of this warp). With WPR = 4 a row's
+// warps leave their sums in `comb` and warp 0 adds them in warp order: with many splits (few requests) the merge is a
+// chain of memory round trips, one per sixteen splits of a warp, and four warps make it one.
+constexpr int AD_MERGE_ROUND = 16;
+#ifndef AD_MERGE_WIDE_FROM
+#define AD_MERGE_WIDE_FROM 8                      // more splits than this: four warps a row
+#endif
+
+template <int WPR>
+__device__ __forceinline__ void ad_merge_row(float* fs, float* comb, const float* o_part, const float* ml_part, size_t row, int n_valid,
+                                             int n_splits, __nv_bfloat16* __restrict__ out, int lane, int sub) {
     const size_t pr0 = row * n_splits;
+    const int d_first = lane * 4;
+    float4 v[AD_MERGE_ROUND];
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < AD_MERGE_ROUND; ++i) {
+        const int s_ = sub + WPR * i;
+        v[i] = (d_first < AT_HD && s_ < n_valid) ? *reinterpret_cast<const float4*>(o_part + (pr0 + s_) * AT_HD + d_first) : zero4;
+    }
     constexpr int PER_LANE = AD_MAX_SPLITS / 32;
     float2 ml[PER_LANE];
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
-        const int s = lane + 32 * i;
-        ml[i] = s < n_valid ? *reinterpret_cast<const float2*>(ml_part + (pr0 + s) * 2) : make_float2(-INFINITY, 0.f);
+        const int s_ = lane + 32 * i;
+        ml[i] = s_ < n_valid ? *reinterpret_cast<const float2*>(ml_part + (pr0 + s_) * 2) : make_float2(-INFINITY, 0.f);
     }
     float M = -INFINITY;
 #pragma unroll
@@ -80,32 +96,55 @@ __device__ __forceinline__ void ad_merge_row(float* fs, const float* o_part, con
     float L = 0.f;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
-        const int s = lane + 32 * i;
+        const int s_ = lane + 32 * i;
         const float f = (ml[i].x == -INFINITY) ? 0.f : exp2f(ml[i].x - M);
-        if (s < n_valid) fs[s] = f;
+        if (s_ < n_valid) fs[s_] = f;
         L += f * ml[i].y;
     }
     L = il_warp_sum(L);
     __syncwarp();
     const float inv = 1.f / L;
-    for (int d = lane * 4; d < AT_HD; d += 128) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < n_valid; s0 += 16) {
-            float4 v[16];
+    for (int d = d_first; d < AT_HD; d += 128) {
+        float4 acc = zero4;
+        for (int i0 = 0; sub + WPR * i0 < n_valid; i0 += AD_MERGE_ROUND) {
+            if (d != d_first || i0 != 0) {        // (the first round is on its way since the start)
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                v[i] = s0 + i < n_valid ? *reinterpret_cast<const float4*>(o_part + (pr0 + s0 + i) * AT_HD + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int i = 0; i < AD_MERGE_ROUND; ++i) {
+                    const int s_ = sub + WPR * (i0 + i);
+                    v[i] = s_ < n_valid ? *reinterpret_cast<const float4*>(o_part + (pr0 + s_) * AT_HD + d) : zero4;
+                }
+            }
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {        // in split order: the same sum whatever the chunking
-                const float f = s0 + i < n_valid ? fs[s0 + i] : 0.f;
+            for (int i = 0; i < AD_MERGE_ROUND; ++i) {    // in the order of the warp's splits: the same sum whatever the round
+                const int s_ = sub + WPR * (i0 + i);
+                const float f = s_ < n_valid ? fs[s_] : 0.f;
                 acc.x += f * v[i].x;
                 acc.y += f * v[i].y;
                 acc.z += f * v[i].z;
                 acc.w += f * v[i].w;
             }
         }
-        const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
-        *reinterpret_cast<uint2*>(out + row * AT_HD + d) = make_uint2(a, b);
+        if (WPR == 1) {
+            const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(out + row * AT_HD + d) = make_uint2(a, b);
+        } else {
+            *reinterpret_cast<float4*>(comb + sub * AT_HD + d) = acc;
+        }
+    }
+    if (WPR > 1) {
+        __syncthreads();                          // a block is one row: all its warps are here
+        if (sub == 0) {
+            for (int d = d_first; d < AT_HD; d += 128) {
+                float4 acc = *reinterpret_cast<const float4*>(comb + d);
+#pragma unroll
+                for (int w = 1; w < WPR; ++w) {
+                    const float4 t = *reinterpret_cast<const float4*>(comb + w * AT_HD + d);
+                    acc.x += t.x, acc.y += t.y, acc.z += t.z, acc.w += t.w;
+                }
+                const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
+                *reinterpret_cast<uint2*>(out + row * AT_HD + d) = make_uint2(a, b);
+            }
+        }
     }
     __syncwarp();
 }
@@ -383,13 +422,15 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     }
 }
 
-// The merge: one warp per (token, head).
+// The merge: WPR warps per (token, head) row - one where the splits are few, the four of a block where they are many.
+template <int WPR>
 __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_part, const float* ml_part,
                                                                 const int* __restrict__ entry_kvlen, int nh, int n_rows, int window,
                                                                 int pages_per_split, int n_splits, __nv_bfloat16* __restrict__ out) {
     __shared__ float fs[4][AD_MAX_SPLITS];
+    __shared__ __align__(16) float comb[WPR > 1 ? WPR * AT_HD : 4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 4 + warp;        // = e * nh + head
+    const int row = blockIdx.x * (4 / WPR) + warp / WPR;      // = e * nh + head
     // the lengths come with the step's descriptors, not from the kernel before: read them while that one still runs
     const int kvlen = row < n_rows ? entry_kvlen[row / nh] : 1;
     const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
@@ -400,10 +441,11 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
     il_pdl_wait();
     if (row >= n_rows) return;
     if (kvlen <= 0) {                             // no keys: the output is zero
-        for (int d = lane * 4; d < AT_HD; d += 128) *reinterpret_cast<uint2*>(out + (size_t)row * AT_HD + d) = make_uint2(0u, 0u);
+        if (warp % WPR == 0)
+            for (int d = lane * 4; d < AT_HD; d += 128) *reinterpret_cast<uint2*>(out + (size_t)row * AT_HD + d) = make_uint2(0u, 0u);
         return;
     }
-    ad_merge_row(fs[warp], o_part, ml_part, (size_t)row, n_valid, n_splits, out, lane);
+    ad_merge_row<WPR>(fs[warp], comb, o_part, ml_part, (size_t)row, n_valid, n_splits, out, lane, warp % WPR);
 }
 
 // Launches both kernels. Scratch: o_part float32 [n_decode*nh*n_splits*head_dim], ml_part [n_decode*nh*n_splits*2].
@@ -433,8 +475,13 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
         scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status);
     const int n_rows = n_decode * nh;
-    IL_LAUNCH(attn_decode_merge_kernel, (n_rows + 3) / 4, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window, pages_per_split,
-                                                                  n_splits, (__nv_bfloat16*)out);
+    if (n_splits > AD_MERGE_WIDE_FROM) {
+        IL_LAUNCH(attn_decode_merge_kernel<4>, n_rows, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window,
+                  pages_per_split, n_splits, (__nv_bfloat16*)out);
+    } else {
+        IL_LAUNCH(attn_decode_merge_kernel<1>, (n_rows + 3) / 4, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows,
+                  window, pages_per_split, n_splits, (__nv_bfloat16*)out);
+    }
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

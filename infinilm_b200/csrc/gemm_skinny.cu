@@ -380,6 +380,13 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_resid_kernel(con
         wrow[h] = W + (size_t)n * ldw;
     }
     il_pdl_begin();
+    // What the epilogue adds to - the residual, the norm's weight, the bias of this thread's (row, column) - is asked for
+    // now: read after the main loop it cost the kernel a round trip to memory at its very end.
+    const int e_nl = threadIdx.x & 15, e_m = threadIdx.x >> 4, e_n = n0 + e_nl;
+    const bool e_live = (int)threadIdx.x < NT * 8 * 16 && e_m < M && e_n < N;
+    const float e_resid = e_live ? resid[(size_t)e_m * N + e_n] : 0.f;
+    const float e_w = e_live ? il_load_any(norm_w, norm_w_kind, e_n) : 0.f;
+    const float e_bias = (e_live && bias) ? bias[e_n] : 0.f;
     const __nv_bfloat16* xrow[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) xrow[t] = (t * 8 + r < M) ? x + (size_t)(t * 8 + r) * ldx : nullptr;
@@ -421,18 +428,18 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_resid_kernel(con
     // one thread per (row, column): 16 consecutive lanes share a row and add up its squares by shuffles; warps beyond the
     // NT * 8 * 16 pairs have nothing to do and leave as a whole
     if ((int)threadIdx.x >= NT * 8 * 16) return;
-    const int nl = threadIdx.x & 15, m = threadIdx.x >> 4;
-    const int n = n0 + nl;
+    const int nl = e_nl, m = e_m;
+    const int n = e_n;
     const int t = m >> 3, mc = m & 7;
     float h = 0.f;
     if (m < M && n < N) {
         float s0 = 0.f;
 #pragma unroll
         for (int w = 0; w < GS_WARPS; ++w) s0 += part[w][t][nl][mc];
-        const float y = __bfloat162float(__float2bfloat16_rn(alpha * s0 + (bias ? bias[n] : 0.f)));
-        h = resid[(size_t)m * N + n] + bscale * y;
+        const float y = __bfloat162float(__float2bfloat16_rn(alpha * s0 + e_bias));
+        h = e_resid + bscale * y;
         resid[(size_t)m * N + n] = h;
-        xw[(size_t)m * N + n] = __float2bfloat16_rn(h * il_load_any(norm_w, norm_w_kind, n));
+        xw[(size_t)m * N + n] = __float2bfloat16_rn(h * e_w);
     }
     float sq = h * h;
     sq += __shfl_xor_sync(0xffffffffu, sq, 8);

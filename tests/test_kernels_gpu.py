@@ -385,7 +385,7 @@ def test_attention_prefill_tc5_late_maximum(cuda_device):
 
 @pytest.mark.parametrize("nh,nkv,hd", SHAPES)
 @pytest.mark.parametrize("window", [None, 40])
-@pytest.mark.parametrize("splits", [1, 3, 7])
+@pytest.mark.parametrize("splits", [1, 3, 7, 13])
 def test_attention_decode_bf16(cuda_device, nh, nkv, hd, window, splits):
     starts = [0, 15, 16, 200, 63, 64]
     c = _attn_case("bfloat16", nh, nkv, hd, starts, [1] * len(starts), window, 12, dominate=True)
@@ -417,6 +417,26 @@ def test_attention_decode_bf16(cuda_device, nh, nkv, hd, window, splits):
     ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
                          window, 0, splits, o_part, ml_part)
     close(out.cpu(), c["ref"], "bfloat16")
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 2, 128), (16, 2, 64), (5, 1, 48), (4, 2, 256)])
+@pytest.mark.parametrize("splits", [9, 33, 70, 128])
+def test_attention_decode_many_splits(cuda_device, nh, nkv, hd, splits):
+    """Many splits (few requests, long contexts): the merge then runs four warps a row, each over every fourth split,
+    in rounds of sixteen. Rows of 1,200, 700 and 16 keys, so that some splits of a row are empty."""
+    starts = [1199, 699, 15]
+    c = _attn_case("bfloat16", nh, nkv, hd, starts, [1] * len(starts), None, 21, dominate=True)
+    E = c["E"]
+    out = torch.full((E, nh * hd), float("nan"), device="cuda", dtype=torch.bfloat16)
+    o_part = torch.full((E * nh * splits * hd,), float("nan"), device="cuda")
+    ml_part = torch.full((E * nh * splits * 2,), float("nan"), device="cuda")
+    for pps in (0, (75 + splits - 1) // splits):
+        out.fill_(float("nan"))
+        ops.attention_decode(c["qkv"], out, c["cache"], c["bt"], c["kvlen"], E, c["page"], nh, nkv, hd, 1 / math.sqrt(hd),
+                             None, pps, splits, o_part, ml_part, kv_map=ops.kv_tensor_map(c["cache"]))
+        torch.cuda.synchronize()
+        assert int(ops.stream_status("cuda:0").item()) == 0
+        close(out.cpu(), c["ref"], "bfloat16")
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (32, 2, 128), (6, 3, 64)])
