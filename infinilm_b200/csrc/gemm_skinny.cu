@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32, 2) gemm_skinny_kernel(const __n
             if (GLU) s1 += part[w][0][t][nl + 8][mc];
         }
         const float an = GLU ? __fmul_rn(alpha, rstd_s[m]) : alpha;     // the norm's 1/rms, where the activations came without it
-        float y = __fmaf_rn(an, s0, bias ? bias[n] : 0.f);      // spelled out: the same bits as gemm_stream's epilogue
+        float y = __fmaf_rn(an, s0, bias ? bias[n] : 0.f);      // spelled out as one fused multiply-add: the same bits from every build of this line
         if (GLU) {
             const float u = __fmaf_rn(an, s1, bias ? bias[N + n] : 0.f);
             y = il_silu_mul_fast(y, u);
