@@ -62,3 +62,18 @@ def test_write_random_model_and_missing_arguments(tmp_path, capsys):
 def test_trace_run_help_runs_without_a_gpu():
     p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--help"], capture_output=True, text=True, timeout=120)
     assert p.returncode == 0 and "--max-tokens" in p.stdout and "--dtype" in p.stdout
+
+
+def _bench(*args):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return subprocess.run([sys.executable, os.path.join(root, "bench.py"), *args], capture_output=True, text=True, timeout=120)
+
+
+def test_bench_answers_without_a_gpu_where_it_runs_nothing():
+    """More than one GPU: one line that says so and exit code 2. The reference arm: its `unavailable` line and exit code 0."""
+    p = _bench("--gpus", "2", "--steps", "4", "--warmup", "3")
+    assert p.returncode == 2 and len(p.stdout.strip().splitlines()) == 1 and "one GPU" in p.stdout
+    p = _bench("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3")
+    assert p.returncode == 0
+    line = json.loads(p.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and line["unavailable"]
