@@ -234,21 +234,10 @@ class StepRunner:
         self.fast_steps += 1
         return gs.logits[:E]
 
-    # -- the step ----------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the order of
-        `entries` and of each entry's `want`.
-
-        A token given as -(1 + i) is not known to the host yet: it is taken from `device_tokens[i]`
-        (int32 on the device, e.g. what the sampler drew in the step before) when the step runs."""
-        if not entries:
-            return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.device)
-        last, self._last_decode = self._last_decode, None
-        if last is not None:
-            logits = self._follow_decode(last, entries, device_tokens)
-            if logits is not None:
-                return logits
-        # ---- checks on whole columns (a fault is then looked up entry by entry, for the message) ------------------
+    # -- a step's entries as columns, checked --------------------------------------------------------
+    def _columns(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor]) -> "_Columns":
+        """The entries' numbers as arrays, one element an entry (or a token, or a wanted place), and every check that
+        needs no page: made on whole columns; a fault is then looked up entry by entry, for the message."""
         vocab = self.model.vocab
         E = len(entries)
         seqs = [e.seq for e in entries]
@@ -291,6 +280,54 @@ class StepRunner:
                 j = int(np.argmax(bad))
                 i = int(np.searchsorted(want_off, j, side="right")) - 1
                 raise StepError(f"entry {i} ({seqs[i].seq_id!r}): wanted place {int(want[j])} is outside its {int(n_tok[i])} tokens")
+        return _Columns(E, seqs, n_tok, start, T, tokens, tok_off, n_want_of, want_off, want)
+
+    # -- whether a step is replayed as a graph -------------------------------------------------------
+    def _replay_key(self, c: "_Columns", n_decode: int, widths: Dict[int, int]):
+        """A step can be replayed as a CUDA graph when its launches and the addresses they read depend on nothing but a
+        key. A decode-only step that wants every row: the batch is padded to a bucket of entries and of block-table
+        width. A step with prompt portions, each entry wanting at most one row: the single tokens are padded to a
+        bucket, the number of portions and of their tokens is part of the key (kernels that are launched per tile of
+        a portion are given a bound on the tiles that the key fixes), and the key must have been seen before - a
+        serving run that cuts long prompts into equal portions repeats it, arbitrary mixes do not.
+        Returns (key or None, entries and tokens with the padding, block-table widths)."""
+        E, T, n_want_of = c.E, c.T, c.n_want_of
+        if not (self.use_graphs and self.tap is None and self.model.graph_safe):
+            return None, E, T, widths
+        if n_decode == E and int(n_want_of.min()) == 1 and int(n_want_of.max()) == 1:
+            Ep = _bucket(E, _ENTRY_BUCKETS)
+            widths = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
+            return (Ep, tuple(sorted(widths.items()))), Ep, Ep, widths
+        single_want = n_want_of[c.n_tok == 1]
+        if self.graph_prompts and int(n_want_of.max()) <= 1 and (single_want.size == 0 or int(single_want.min()) == 1):
+            Dp = _bucket(n_decode, _ENTRY_BUCKETS) if n_decode else 0
+            bw = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
+            key = ("portions", Dp, E - n_decode, T - n_decode, tuple(sorted(bw.items())))
+            seen = self._shapes_seen.get(key, 0)
+            if seen >= self.GRAPH_AFTER:
+                return key, Dp + E - n_decode, Dp + T - n_decode, bw
+            if len(self._shapes_seen) > 4096:
+                self._shapes_seen.clear()
+            self._shapes_seen[key] = seen + 1
+        return None, E, T, widths
+
+    # -- the step ----------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [wanted, vocab] on the device, in the order of
+        `entries` and of each entry's `want`.
+
+        A token given as -(1 + i) is not known to the host yet: it is taken from `device_tokens[i]`
+        (int32 on the device, e.g. what the sampler drew in the step before) when the step runs."""
+        if not entries:
+            return torch.empty((0, self.model.vocab), dtype=torch.float32, device=self.device)
+        last, self._last_decode = self._last_decode, None
+        if last is not None:
+            logits = self._follow_decode(last, entries, device_tokens)
+            if logits is not None:
+                return logits
+        c = self._columns(entries, device_tokens)
+        E, seqs, n_tok, start, T, tokens, tok_off = c.E, c.seqs, c.n_tok, c.start, c.T, c.tokens, c.tok_off
+        n_want_of, want_off, want = c.n_want_of, c.want_off, c.want
         # Reserve pages for all entries, or for none.
         new_len = (start + n_tok).tolist()
         if not self.cache.can_reserve(list(zip(seqs, new_len))):
@@ -309,35 +346,8 @@ class StepRunner:
         tbl_ptr = np.array([[s_.tables[g].address() for s_ in seqs] for g in paged], dtype=np.uint64).reshape(len(paged), E)
         widths = {g: max(1, int(tbl_len[k].max())) for k, g in enumerate(paged)}
 
-        # A step can be replayed as a CUDA graph when its launches and the addresses they read depend on nothing but a
-        # key. A decode-only step that wants every row: the batch is padded to a bucket of entries and of block-table
-        # width. A step with prompt portions, each entry wanting at most one row: the single tokens are padded to a
-        # bucket, the number of portions and of their tokens is part of the key (kernels that are launched per tile of
-        # a portion are given a bound on the tiles that the key fixes), and the key must have been seen before - a
-        # serving run that cuts long prompts into equal portions repeats it, arbitrary mixes do not.
-        graph_key = None
-        Ep, Tp, pad_at, n_want_fixed = E, T, E, -1
-        if self.use_graphs and self.tap is None and self.model.graph_safe:
-            single_want = n_want_of[n_tok == 1]
-            if n_decode == E and int(n_want_of.min()) == 1 and int(n_want_of.max()) == 1:
-                Ep = _bucket(E, _ENTRY_BUCKETS)
-                widths = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
-                Tp = Ep
-                graph_key = (Ep, tuple(sorted(widths.items())))
-            elif (self.graph_prompts and int(n_want_of.max()) <= 1 and (single_want.size == 0 or int(single_want.min()) == 1)):
-                Dp = _bucket(n_decode, _ENTRY_BUCKETS) if n_decode else 0
-                bw = {g: _bucket_pow2(w, 16) for g, w in widths.items()}
-                key = ("portions", Dp, E - n_decode, T - n_decode, tuple(sorted(bw.items())))
-                seen = self._shapes_seen.get(key, 0)
-                if seen < self.GRAPH_AFTER:
-                    if len(self._shapes_seen) > 4096:
-                        self._shapes_seen.clear()
-                    self._shapes_seen[key] = seen + 1
-                else:
-                    graph_key, widths = key, bw
-                    Ep, Tp = Dp + E - n_decode, Dp + T - n_decode
-            if graph_key is not None:
-                pad_at, n_want_fixed = n_decode, Ep
+        graph_key, Ep, Tp, widths = self._replay_key(c, n_decode, widths)
+        pad_at, n_want_fixed = (n_decode, Ep) if graph_key is not None else (E, -1)
         n_want = n_want_fixed if graph_key is not None else int(want_off[E])
         n_neg = int((tokens < 0).sum())
         n_patch = Tp if graph_key is not None else n_neg          # a replayed step's buffer is sized once, for any number
@@ -461,6 +471,21 @@ class StepRunner:
         self.steps_run += 1
         self.tokens_run += T
         return logits
+
+
+@dataclass
+class _Columns:
+    """A step's entries as arrays (`StepRunner._columns`)."""
+    E: int
+    seqs: list
+    n_tok: np.ndarray                             # tokens an entry brings
+    start: np.ndarray                             # tokens it has in the cache
+    T: int
+    tokens: np.ndarray                            # all tokens, entry after entry (int64; below 0: still on the device)
+    tok_off: np.ndarray                           # [E + 1] where an entry's tokens start
+    n_want_of: np.ndarray
+    want_off: np.ndarray                          # [E + 1] where an entry's wanted places start
+    want: np.ndarray                              # all wanted places, entry after entry
 
 
 @dataclass
