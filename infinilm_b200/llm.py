@@ -192,21 +192,27 @@ class LLM:
     def generate(self, prompts: Union[str, List[str], None] = None, messages=None,
                  sampling_params: Optional[SamplingParams] = None, use_tqdm: bool = False,
                  prompt_token_ids: Optional[List[List[int]]] = None) -> List[RequestOutput]:
+        """InfiniLM's `LLM.generate` (`python/infinilm/llm/llm.py:428-501`): prompts or conversations in, one
+        `RequestOutput` each out, in order. Beside it: `prompt_token_ids` (token ids instead of text), and
+        `sampling_params` may be a list, one for each prompt."""
         if isinstance(prompts, str):
             prompts = [prompts]
+
+        def sp_of(i: int):
+            return sampling_params[i] if isinstance(sampling_params, (list, tuple)) else sampling_params
         reqs: List[Request] = []
         if prompt_token_ids is not None:
-            for ids in prompt_token_ids:
-                reqs.append(self.add_request(ids, sampling_params))
+            for i, ids in enumerate(prompt_token_ids):
+                reqs.append(self.add_request(ids, sp_of(i)))
         elif messages is not None:
             if messages and isinstance(messages[0], dict):
                 messages = [messages]
-            for conv in messages:
+            for i, conv in enumerate(messages):
                 text = self.tokenizer.apply_chat_template(conv, add_generation_prompt=True, tokenize=False)
-                reqs.append(self.add_request(self.tokenize(text), sampling_params, prompt=text))
+                reqs.append(self.add_request(self.tokenize(text), sp_of(i), prompt=text))
         elif prompts is not None:
-            for text in prompts:
-                reqs.append(self.add_request(self.tokenize(text), sampling_params, prompt=text))
+            for i, text in enumerate(prompts):
+                reqs.append(self.add_request(self.tokenize(text), sp_of(i), prompt=text))
         else:
             raise ValueError("generate needs prompts, messages or prompt_token_ids")
         pbar = None

@@ -49,6 +49,17 @@ def test_greedy_generation_matches_plain(cuda_device):
             ids.append(t)
 
 
+def test_sampling_parameters_may_differ_from_prompt_to_prompt(cuda_device):
+    raw = tiny_a()
+    w = make_weights(raw, 0)
+    prompts = [random_ids(n, raw["vocab_size"], 40 + n) for n in (7, 21, 4)]
+    llm = LLM.from_tensors(config_from_json(raw), w, dtype="float32", num_blocks=16, block_size=16, max_batch_size=3)
+    sps = [SamplingParams(top_k=1, max_tokens=m, ignore_eos=True) for m in (3, 11, 6)]
+    outs = llm.generate(prompt_token_ids=prompts, sampling_params=sps)
+    for p, o, m in zip(prompts, outs, (3, 11, 6)):
+        assert o.outputs[0].token_ids == plain_model.greedy_generate(raw, w, p, m)
+
+
 def test_eos_stops_generation(cuda_device):
     raw = tiny_a()
     w = make_weights(raw, 0)
