@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
     float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap kv_page_map,
-    int use_tma, int* __restrict__ status) {
+    int use_tma, int* __restrict__ status, __nv_bfloat16* __restrict__ out_direct) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     // Lengths, block tables and the pages of earlier tokens do not come from the kernel before this one (it writes q and
@@ -170,7 +170,16 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     const int kvlen = entry_kvlen[e];
-    if (kvlen <= 0) return;                       // no keys: the merge kernel writes zeros for this row
+    if (kvlen <= 0) {                             // no keys: the merge kernel writes zeros for this row, or, where there is none, this block
+        if (out_direct) {
+            const int h0 = g * G + rt * 16, rv = min(16, G - rt * 16);
+            for (int idx = threadIdx.x; idx < rv * (AT_HD / 4); idx += AD_WARPS * 32) {
+                const int r = idx / (AT_HD / 4), d = (idx - r * (AT_HD / 4)) * 4;
+                *reinterpret_cast<uint2*>(out_direct + ((size_t)e * nh + h0 + r) * AT_HD + d) = make_uint2(0u, 0u);
+            }
+        }
+        return;
+    }
     const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
     const int first_page = lo / AD_PAGE, last_page = (kvlen - 1) / AD_PAGE;
     // pages_per_split 0: this request's pages are divided evenly over the splits
@@ -406,6 +415,22 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
             acc.w += v.w;
         }
         const size_t pr = ((size_t)e * nh + head0 + r) * n_splits + split;
+        if (out_direct) {
+            // one split: nothing to merge, the row is final. The same arithmetic as the merge of a single part (factor 1,
+            // the sum over the warps in warp order, one division), so the bits do not depend on which kernel finished the row.
+            float M = -INFINITY, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+#pragma unroll
+            for (int w = 0; w < AD_WARPS; ++w) {
+                const float mw = sm_ml[(w * 16 + r) * 2];
+                L += ((mw == -INFINITY) ? 0.f : exp2f(mw - M)) * sm_ml[(w * 16 + r) * 2 + 1];
+            }
+            const float inv = 1.f / L;
+            const uint32_t a = at_pack_bf16(acc.x * inv, acc.y * inv), b = at_pack_bf16(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(out_direct + pr * AT_HD + d) = make_uint2(a, b);
+            continue;
+        }
         *reinterpret_cast<float4*>(o_part + pr * AT_HD + d) = acc;
         if (d == 0) {
             float M = -INFINITY, L = 0.f;
@@ -448,7 +473,7 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
     ad_merge_row<WPR>(fs[warp], comb, o_part, ml_part, (size_t)row, n_valid, n_splits, out, lane, warp % WPR);
 }
 
-// Launches both kernels. Scratch: o_part float32 [n_decode*nh*n_splits*head_dim], ml_part [n_decode*nh*n_splits*2].
+// Launches the attention kernel and, for more than one split, the merge. Scratch: o_part float32 [n_decode*nh*n_splits*head_dim], ml_part [n_decode*nh*n_splits*2].
 static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
                      const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
                      int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
@@ -473,7 +498,12 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     dim3 grid(n_splits, nkv * row_tiles, n_decode);
     IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, AD_SMEM, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
-        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status);
+        scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status,
+        n_splits == 1 ? (__nv_bfloat16*)out : (__nv_bfloat16*)nullptr);
+    if (n_splits == 1) {                          // every row is final as the attention kernel leaves it: no merge
+        IL_LAUNCH_CHECK();
+        return IL_OK;
+    }
     const int n_rows = n_decode * nh;
     if (n_splits > AD_MERGE_WIDE_FROM) {
         IL_LAUNCH(attn_decode_merge_kernel<4>, n_rows, 128, 0, stream, (const float*)o_part, (const float*)ml_part, entry_kvlen, nh, n_rows, window,

@@ -264,7 +264,7 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
                      head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
                      o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None) -> None:
     """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each), then the merge of
-    the splits (a second launch). A row whose length is 0 gets zeros; a block-table entry below 0 is never followed.
+    the splits (a second launch; with n_splits = 1 there is none and the attention kernel writes `out` itself). A row whose length is 0 gets zeros; a block-table entry below 0 is never followed.
     pages_per_split 0: each request's pages are divided evenly over the n_splits splits.
     kv_map: the cache's tensor map from `kv_tensor_map` (pages then come in by TMA tensor copies).
     Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
@@ -290,7 +290,8 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
              _stream()), "attention_decode")
-    count_launches(1)                             # the merge kernel
+    if n_splits > 1:
+        count_launches(1)                         # the merge kernel (a single split needs none: the attention kernel finishes the rows)
 
 
 _resident = {}
